@@ -1,0 +1,73 @@
+// Shared device/host helpers of libfgc_b200 (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "fgc_b200.h"
+
+#define FGC_FULL_MASK 0xffffffffu
+
+// Launch-error check usable inside extern "C" entry points: returns the CUDA
+// error code to the caller (never exits, never synchronises).
+#define FGC_RETURN_IF_CUDA(expr)                 \
+    do {                                         \
+        cudaError_t fgc_e_ = (expr);             \
+        if (fgc_e_ != cudaSuccess) return (int)fgc_e_; \
+    } while (0)
+
+#define FGC_CHECK_LAUNCH() FGC_RETURN_IF_CUDA(cudaGetLastError())
+
+namespace fgc {
+
+__host__ __device__ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Monotone float -> uint32 key (total order incl. negatives) for atomicMax/Min.
+__device__ __forceinline__ uint32_t float_to_ordered(float f)
+{
+    uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__host__ __device__ __forceinline__ float ordered_to_float(uint32_t k)
+{
+    uint32_t b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+#ifdef __CUDA_ARCH__
+    return __uint_as_float(b);
+#else
+    union { uint32_t u; float f; } cv;
+    cv.u = b;
+    return cv.f;
+#endif
+}
+
+__device__ __forceinline__ bool is_finite_bits(float f)
+{
+    return (__float_as_uint(f) & 0x7f800000u) != 0x7f800000u;
+}
+
+__device__ __forceinline__ uint32_t lanemask_lt()
+{
+    uint32_t m;
+    asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+    return m;
+}
+__device__ __forceinline__ uint32_t lanemask_le()
+{
+    uint32_t m;
+    asm("mov.u32 %0, %%lanemask_le;" : "=r"(m));
+    return m;
+}
+
+// Index of the row split that contains point v: number of entries rs[1..] <= v
+// (what the reference finds by a linear scan, bin_by_coordinates_cpu.cpp:68-74).
+__device__ __forceinline__ int row_split_of(const int64_t *__restrict__ rs, int n_rs, int64_t v)
+{
+    int lo = 1, hi = n_rs;  // first index in [1, n_rs) with rs[idx] > v
+    while (lo < hi) {
+        int mid = (lo + hi) >> 1;
+        if (rs[mid] > v) hi = mid; else lo = mid + 1;
+    }
+    return lo - 1;
+}
+
+}  // namespace fgc

@@ -1,0 +1,100 @@
+// Gradient of the kNN squared distances w.r.t. the coordinates (sm_100a).
+//
+//   G[i,v] = -sum_k 2 g[i,k] (x[n,v] - x[i,v])        (the row's own term)
+//   G[n,v] +=        2 g[i,k] (x[n,v] - x[i,v])        (scattered to n = idx[i,k] >= 0)
+// as in extensions/binned_select_knn_grad_cpu.cpp:6-93 (CUDA twin
+// extensions/binned_select_knn_grad_cuda_kernel.cu:25-88).
+//
+// One warp per row: the lanes take the K slots (coalesced idx / grad loads), the
+// row's own term is reduced inside the warp and leaves as ONE add per
+// coordinate, the neighbour term leaves as one reduction (red.global.add.f32)
+// per slot and coordinate.
+#include "fgc_common.cuh"
+
+namespace fgc {
+
+constexpr int kBwdWarps = 8;
+
+template <int D>
+__global__ void __launch_bounds__(kBwdWarps * 32)
+k_knn_bwd(const float *__restrict__ grad_distsq, const int64_t *__restrict__ idx,
+          const float *__restrict__ coords, int n_vert, int K, int n_coords_rt,
+          float *__restrict__ out)
+{
+    const int lane = threadIdx.x & 31;
+    const int i = blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
+    if (i >= n_vert) return;
+    const int nc = D > 0 ? D : n_coords_rt;
+    constexpr int DM = D > 0 ? D : 1;
+    if (D > 0) {
+        float xi[DM], self[DM];
+#pragma unroll
+        for (int v = 0; v < DM; v++) { xi[v] = __ldg(coords + (size_t)i * nc + v); self[v] = 0.f; }
+        for (int k0 = 0; k0 < K; k0 += 32) {
+            const int k = k0 + lane;
+            if (k < K) {
+                const int64_t n = idx[(size_t)i * K + k];
+                if (n >= 0 && n < n_vert) {
+                    const float g2 = 2.f * grad_distsq[(size_t)i * K + k];
+#pragma unroll
+                    for (int v = 0; v < DM; v++) {
+                        const float c = g2 * (__ldg(coords + (size_t)n * nc + v) - xi[v]);
+                        self[v] -= c;
+                        atomicAdd(out + (size_t)n * nc + v, c);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < DM; v++) {
+            float s = self[v];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FGC_FULL_MASK, s, o);
+            if (lane == 0) atomicAdd(out + (size_t)i * nc + v, s);
+        }
+    } else {
+        // any number of coordinates: one coordinate at a time
+        for (int v = 0; v < nc; v++) {
+            const float xi = __ldg(coords + (size_t)i * nc + v);
+            float self = 0.f;
+            for (int k = lane; k < K; k += 32) {
+                const int64_t n = idx[(size_t)i * K + k];
+                if (n >= 0 && n < n_vert) {
+                    const float c = 2.f * grad_distsq[(size_t)i * K + k] *
+                                    (__ldg(coords + (size_t)n * nc + v) - xi);
+                    self -= c;
+                    atomicAdd(out + (size_t)n * nc + v, c);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) self += __shfl_xor_sync(FGC_FULL_MASK, self, o);
+            if (lane == 0) atomicAdd(out + (size_t)i * nc + v, self);
+        }
+    }
+}
+
+}  // namespace fgc
+
+extern "C" int fgc_binned_knn_bwd(const float *grad_distsq, const int64_t *idx, const float *coords,
+                                  int64_t n_vert, int32_t K, int32_t n_coords,
+                                  float *out_grad_coords, fgc_stream_t stream)
+{
+    using namespace fgc;
+    if (n_vert < 0 || K < 1 || n_coords < 1) return FGC_ERR_BAD_ARGUMENT;
+    if (n_vert > 0x7fffffff) return FGC_ERR_TOO_LARGE;
+    if (n_vert == 0) return FGC_OK;
+    if (!grad_distsq || !idx || !coords || !out_grad_coords) return FGC_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    FGC_RETURN_IF_CUDA(cudaMemsetAsync(out_grad_coords, 0, sizeof(float) * (size_t)n_vert * n_coords, s));
+    const int n = (int)n_vert;
+    const unsigned blocks = (unsigned)((n + kBwdWarps - 1) / kBwdWarps);
+    const int T = kBwdWarps * 32;
+    switch (n_coords) {
+    case 2: k_knn_bwd<2><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords); break;
+    case 3: k_knn_bwd<3><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords); break;
+    case 4: k_knn_bwd<4><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords); break;
+    default: k_knn_bwd<0><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords); break;
+    }
+    FGC_CHECK_LAUNCH();
+    return FGC_OK;
+}

@@ -1,0 +1,142 @@
+"""binned_select_knn -- drop-in for fastgraphcompute.extensions.binned_select_knn.
+
+Same call signature, returned tensors and autograd behaviour as the reference
+(extensions/binned_select_knn.py:12-94 on top of BinnedKNNAutograd,
+extensions/binned_knn_autograd_kernel.cpp:84-253): indices int64 [N,K] with the
+point itself in slot 0 and -1 in unused slots, squared distances float32 [N,K],
+differentiable w.r.t. the coordinates through the distances only.
+"""
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _cabi
+
+# Mean number of points per search-grid cell the library aims for (<= 0: built-in default).
+target_occupancy = 0.0
+# Read the device status word after every forward (one small device->host copy).
+# The reference synchronises several times per call; switching this off makes the
+# call fully asynchronous but turns bad inputs (NaN, malformed row_splits) into
+# silently unwritten outputs.
+check_status = True
+
+
+def _raise_for_status(status):
+    if status & _cabi.STATUS_NONFINITE:
+        raise RuntimeError("BinByCoordinates: input coordinates contain non-finite values")
+    if status & _cabi.STATUS_BAD_ROW_SPLITS:
+        raise RuntimeError("binned_select_knn: row_splits must start at 0, be non-decreasing and "
+                           "end at the number of points (bin boundaries do not match row splits)")
+    if status:
+        raise RuntimeError("binned_select_knn: internal error, status %d" % status)
+
+
+def knn_forward_raw(coords, row_splits, K, direction, tf_compat):
+    """Launch fgc_binned_knn_fwd on prepared tensors; returns (idx, distsq, workspace)."""
+    dev = coords.device
+    n_vert, n_coords = coords.shape
+    idx = torch.empty((n_vert, K), dtype=torch.int64, device=dev)
+    dist = torch.empty((n_vert, K), dtype=torch.float32, device=dev)
+    nbytes = _cabi.lib.fgc_knn_workspace_bytes(n_vert, n_coords, row_splits.numel(), K)
+    if nbytes == 0:
+        if K < 1 or K > _cabi.FGC_MAX_K:
+            raise ValueError("binned_select_knn: K must be in 1..%d, got %d" % (_cabi.FGC_MAX_K, K))
+        raise ValueError("binned_select_knn: unsupported problem size")
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        stream = _cabi.current_stream(dev)
+        _cabi.check(_cabi.lib.fgc_binned_knn_fwd(
+            _cabi.ptr(coords), n_vert, n_coords, _cabi.ptr(row_splits), row_splits.numel(), K,
+            _cabi.ptr(direction), int(bool(tf_compat)), float(target_occupancy), _cabi.ptr(idx),
+            _cabi.ptr(dist), _cabi.ptr(ws), nbytes, stream), "fgc_binned_knn_fwd")
+        if check_status:
+            st = ctypes.c_int32(0)
+            _cabi.check(_cabi.lib.fgc_read_status(_cabi.ptr(ws), ctypes.byref(st), stream),
+                        "fgc_read_status")
+            _raise_for_status(st.value)
+    return idx, dist, ws
+
+
+class _BinnedKNN(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, coords, row_splits, K, direction, tf_compat):
+        idx, dist, _ = knn_forward_raw(coords, row_splits, K, direction, tf_compat)
+        ctx.save_for_backward(idx, coords)
+        ctx.mark_non_differentiable(idx)
+        return idx, dist
+
+    @staticmethod
+    def backward(ctx, grad_idx, grad_dist):
+        idx, coords = ctx.saved_tensors
+        if not ctx.needs_input_grad[0]:
+            return None, None, None, None, None
+        if grad_dist is None:
+            return torch.zeros_like(coords), None, None, None, None
+        grad_dist = grad_dist.to(dtype=torch.float32).contiguous()
+        n_vert, n_coords = coords.shape
+        out = torch.empty_like(coords)
+        with torch.cuda.device(coords.device):
+            _cabi.check(_cabi.lib.fgc_binned_knn_bwd(
+                _cabi.ptr(grad_dist), _cabi.ptr(idx), _cabi.ptr(coords), n_vert, idx.shape[1],
+                n_coords, _cabi.ptr(out), _cabi.current_stream(coords.device)),
+                "fgc_binned_knn_bwd")
+        return out, None, None, None, None
+
+
+def binned_select_knn(K: int, coords: torch.Tensor, row_splits: torch.Tensor,
+                      direction: Optional[torch.Tensor] = None,
+                      n_bins: Optional[torch.Tensor] = None, max_bin_dims: int = 3,
+                      torch_compatible_indices: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """K nearest neighbours inside each row split.
+
+    Args:
+        K: number of neighbours including the point itself.
+        coords: [N, D] coordinates, D >= 2 (converted to float32).
+        row_splits: ragged-tensor row splits; neighbours never cross a split.
+        direction: optional [N] tensor; 0: can only be a neighbour, 1: can only have
+            neighbours, 2: neither.
+        n_bins, max_bin_dims: accepted for compatibility and validated like the
+            reference does.  They tune the reference's internal binning and do not
+            change which points are nearest; this implementation sizes its own
+            search grid from the data.
+        torch_compatible_indices: fill unused slots with the point's own index instead of -1.
+
+    Returns:
+        (indices int64 [N,K], squared distances float32 [N,K]).  Slot 0 is the point
+        itself; the order of the other slots is unspecified, as in the reference.
+    """
+    _cabi.require_cuda(coords, "coords")
+    if coords.dim() != 2:
+        raise ValueError("coords must be [N, D]")
+    if coords.shape[1] == 0:
+        raise ValueError("Input coordinates must have at least one dimension. Got 0 dimensions.")
+    if max_bin_dims == 0:
+        raise ValueError("max_bin_dims must be greater than 0. Got 0.")
+    K = int(K)
+    max_bin_dims = int(max_bin_dims)
+    if max_bin_dims < 0:
+        raise ValueError("max_bin_dims must be greater than 0.")
+    if coords.shape[1] < 2:
+        # the reference supports 2..5 binning dimensions only (binned_select_knn_cpu.cpp:278)
+        raise ValueError("Unsupported number of binning dimensions.")
+    dev = coords.device
+    if not isinstance(row_splits, torch.Tensor):
+        row_splits = torch.tensor(row_splits, dtype=torch.int64, device=dev)
+    if coords.dtype != torch.float32:
+        coords = coords.to(dtype=torch.float32)
+    if n_bins is not None:
+        if not isinstance(n_bins, torch.Tensor):
+            n_bins = torch.tensor(n_bins, dtype=torch.int64)
+        if not bool((n_bins > 0).all()):
+            raise RuntimeError("BinByCoordinates: n_bins must be greater than zero.")
+    coords = coords.contiguous()
+    row_splits = row_splits.to(device=dev, dtype=torch.int64).contiguous()
+    if direction is not None:
+        if direction.numel() == 0:
+            direction = None
+        else:
+            direction = direction.detach().to(device=dev, dtype=torch.int64).contiguous()
+            if direction.numel() != coords.shape[0]:
+                raise ValueError("direction must have one entry per point")
+    return _BinnedKNN.apply(coords, row_splits, K, direction, bool(torch_compatible_indices))

@@ -1,0 +1,198 @@
+/*
+ * fgc_b200.h -- C ABI of libfgc_b200.so, the sm_100a implementation of the
+ * FastGraphCompute spatial-graph hot path (coordinate binning, binned kNN
+ * forward/backward, index_replacer, GravNet neighbour aggregation).
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer unless its name ends in _host.
+ *  - Row-major, contiguous arrays; coordinates fp32, indices int64 (the
+ *    reference's public dtypes), row_splits int64 of length n_rs.
+ *  - The library never allocates or frees device memory and never retains a
+ *    pointer after the call returns.  Outputs and scratch ("workspace") are
+ *    provided by the caller; *_workspace_bytes() says how much.
+ *  - Work is enqueued on `stream` (a cudaStream_t); calls do not synchronise
+ *    unless documented.  The device that owns the pointers must be current.
+ *  - Return value: FGC_OK (0), a negative FGC_ERR_* argument error, or a
+ *    positive cudaError_t value.  Data-dependent problems (non-finite
+ *    coordinates, malformed row_splits) are reported through a status word in
+ *    device memory, read with fgc_read_status().
+ *  - Re-entrant: no global mutable state; concurrent calls on different
+ *    streams/devices are safe as long as they use different workspaces.
+ *
+ * Each entry point names the reference interface it replaces
+ * (paths relative to the FastGraphCompute repository).
+ */
+#ifndef FGC_B200_H
+#define FGC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FGC_OK 0
+#define FGC_ERR_BAD_ARGUMENT (-1)   /* null pointer, negative size, ... */
+#define FGC_ERR_UNSUPPORTED_DIM (-2)/* n_coords < 2 for the kNN (the reference raises for < 2 bin dims) */
+#define FGC_ERR_UNSUPPORTED_K (-3)  /* K < 1 or K > FGC_MAX_K */
+#define FGC_ERR_WORKSPACE (-4)      /* workspace too small / misaligned */
+#define FGC_ERR_TOO_LARGE (-5)      /* n_vert or a bin table exceeds 2^31-1 entries */
+
+/* bits of the device status word */
+#define FGC_STATUS_NONFINITE 1      /* a coordinate is NaN or +-Inf */
+#define FGC_STATUS_BAD_ROW_SPLITS 2 /* row_splits not 0-based, not non-decreasing or not ending at n_vert */
+#define FGC_STATUS_BAD_DMAX 4       /* binning: max coordinate not > 0 after normalisation */
+#define FGC_STATUS_BAD_NBINS 8      /* binning: some n_bins <= 0 */
+#define FGC_STATUS_BAD_BINWIDTH 16  /* binning: bin_width <= 0 */
+#define FGC_STATUS_INTERNAL 32      /* an internal consistency check failed */
+
+#define FGC_MAX_K 257               /* self + 256 neighbours */
+#define FGC_MAX_BIN_DIMS 8          /* coordinate dimensions accepted by fgc_bin_* */
+
+typedef struct CUstream_st *fgc_stream_t; /* == cudaStream_t */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int fgc_version(void);
+
+/* Text for a return value of this library. */
+const char *fgc_error_string(int code);
+
+/* ------------------------------------------------------------------------- */
+/* bin_by_coordinates                                                         */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * Binning parameters derived on the device by fgc_bin_prepare (device-resident
+ * record, 256 bytes; copy it to the host to learn n_bins / bin_width / status).
+ */
+typedef struct fgc_bin_params {
+    int32_t status;                    /* FGC_STATUS_* bits, 0 = fine */
+    int32_t n_coords;
+    float bin_width;                   /* the single, uniform bin width */
+    int32_t reserved0;
+    float shift[FGC_MAX_BIN_DIMS];     /* subtracted from every coordinate (0 if pre_normalized) */
+    int64_t n_bins[FGC_MAX_BIN_DIMS];  /* bins per dimension */
+    uint32_t scratch[2 * FGC_MAX_BIN_DIMS + 2];
+    uint8_t pad[256 - 16 - 4 * FGC_MAX_BIN_DIMS - 8 * FGC_MAX_BIN_DIMS - 4 * (2 * FGC_MAX_BIN_DIMS + 2)];
+} fgc_bin_params;
+
+/*
+ * Step 1 of bin_by_coordinates: one fused pass over the coordinates (finite
+ * check, per-dimension min and max) and the derivation of shift, dmax, n_bins
+ * and bin_width with the reference's fp32 arithmetic.
+ * Replaces the host part of bin_by_coordinates (extensions/bin_by_coordinates.cpp:31-120,
+ * same steps in extensions/bin_by_coordinates.py:33-104).
+ *   bin_width_or_null : [1] fp32 or NULL;  n_bins_or_null : [n_bins_len] int64
+ *   (n_bins_len 1 = scalar repeated, or n_coords) or NULL; at least one is needed.
+ * out_params is written on the device; no synchronisation.
+ */
+int fgc_bin_prepare(const float *coords, int64_t n_vert, int32_t n_coords, int32_t pre_normalized,
+                    const float *bin_width_or_null, const int64_t *n_bins_or_null,
+                    int32_t n_bins_len, fgc_bin_params *out_params, fgc_stream_t stream);
+
+/*
+ * Step 2: per-point bin assignment and histogram.
+ * Replaces bin_by_coordinates_cuda_fn / calc (extensions/bin_by_coordinates_cuda_kernel.cu:24-172;
+ * CPU twin extensions/bin_by_coordinates_cpu.cpp:7-152).
+ *   out_bin_idx  [n_vert, n_coords+1] = [row-split index, bin index per dimension]
+ *   out_flat     [n_vert]  flat bin id (last dimension fastest, row split slowest)
+ *   out_n_per_bin[n_total_bins] (must be zeroed by the caller) or NULL when
+ *                calc_n_per_bin == 0
+ * n_total_bins = prod(n_bins) * (n_rs - 1) as read back from the parameters.
+ */
+int fgc_bin_assign(const float *coords, int64_t n_vert, int32_t n_coords,
+                   const int64_t *row_splits, int64_t n_rs, const fgc_bin_params *params,
+                   int32_t calc_n_per_bin, int64_t n_total_bins, int64_t *out_bin_idx,
+                   int64_t *out_flat, int64_t *out_n_per_bin, fgc_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* binned_select_knn                                                          */
+/* ------------------------------------------------------------------------- */
+
+/* Scratch bytes fgc_binned_knn_fwd needs for this problem size (0 on bad arguments). */
+size_t fgc_knn_workspace_bytes(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K);
+
+/*
+ * k-nearest-neighbour search inside each row split (forward).
+ * Replaces BinnedKNNAutograd::forward (extensions/binned_knn_autograd_kernel.cpp:85-209)
+ * including its callees binned_select_knn_cuda_fn (extensions/binned_select_knn_cuda_kernel.cu:252-384),
+ * index_replacer_cuda_fn and the un-sort scatters: builds its own bin grid,
+ * counting-sorts the points, searches in expanding shells and writes rows in
+ * ORIGINAL order with ORIGINAL ids.
+ *   out_idx   [n_vert, K] int64: slot 0 = the point itself, then its K-1 nearest
+ *             neighbours of the same row split in no particular order, then -1
+ *             (or the point's own id when tf_compat != 0) where the row split
+ *             has fewer than K eligible points.
+ *   out_distsq[n_vert, K] fp32 squared distances (0 for slot 0 and empty slots),
+ *             accumulated over the dimensions in order, one rounding per
+ *             operation, as extensions/binned_select_knn_cpu.cpp:10-19.
+ *   direction_or_null [n_vert] int64: 0 may only BE a neighbour, 1 may only HAVE
+ *             neighbours, 2 neither, other values: no restriction.
+ *   target_occupancy : mean points per grid cell to aim for (<= 0: library default).
+ * The first 4 bytes of the workspace hold the status word (fgc_read_status).
+ */
+int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,
+                       const int64_t *row_splits, int64_t n_rs, int32_t K,
+                       const int64_t *direction_or_null, int32_t tf_compat,
+                       float target_occupancy, int64_t *out_idx, float *out_distsq,
+                       void *workspace, size_t workspace_bytes, fgc_stream_t stream);
+
+/*
+ * Copies the status word at the start of a workspace / fgc_bin_params to the
+ * host and waits for the stream (the only synchronising call of the library).
+ */
+int fgc_read_status(const void *workspace_or_params, int32_t *status_host, fgc_stream_t stream);
+
+/*
+ * Gradient of the squared distances with respect to the coordinates (backward).
+ * Replaces binned_select_knn_grad_cuda_fn (extensions/binned_select_knn_grad_cuda_kernel.cu:90-164;
+ * CPU twin extensions/binned_select_knn_grad_cpu.cpp:96-164):
+ *   G[i] = -sum_k 2 g[i,k] (x[n]-x[i]),  G[n] += 2 g[i,k] (x[n]-x[i]),  n = idx[i,k] >= 0.
+ * out_grad_coords [n_vert, n_coords] is overwritten.
+ */
+int fgc_binned_knn_bwd(const float *grad_distsq, const int64_t *idx, const float *coords,
+                       int64_t n_vert, int32_t K, int32_t n_coords, float *out_grad_coords,
+                       fgc_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* index_replacer                                                             */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * out[i] = in[i] < 0 ? in[i] : (in[i] >= n_replacements ? replacements[i] : replacements[in[i]]).
+ * Replaces index_replacer_cuda_fn (extensions/index_replacer_cuda_kernel.cu:9-58; CPU twin
+ * extensions/index_replacer_cpu.cpp:7-26).  The out-of-range branch reads replacements at
+ * the element's POSITION, as the reference does; positions beyond the table keep in[i].
+ */
+int fgc_index_replacer(const int64_t *to_be_replaced, int64_t n, const int64_t *replacements,
+                       int64_t n_replacements, int64_t *out, fgc_stream_t stream);
+
+/* ------------------------------------------------------------------------- */
+/* GravNet neighbour aggregation                                              */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * Fused steps 4-7 of GravNetOp.forward (fastgraphcompute/gnn_ops.py:90-102, with
+ * select_with_default of extensions/oc_helper.py:232-271): weights exp(-10 distsq),
+ * gather of neighbour rows (-1 -> 0), mean over the K slots (divided by K) and
+ * max over the K slots.  out_argmax [n_vert, P] int32 records the slot of the max
+ * for the backward pass.
+ */
+int fgc_gravnet_aggregate_fwd(const float *prop, const int64_t *idx, const float *distsq,
+                              int64_t n_vert, int32_t K, int32_t P, float *out_mean,
+                              float *out_max, int32_t *out_argmax, fgc_stream_t stream);
+
+/*
+ * Backward of the aggregation (what autograd derives for gnn_ops.py:90-102).
+ * out_d_prop [n_vert, P] and out_d_distsq [n_vert, K] are overwritten.
+ */
+int fgc_gravnet_aggregate_bwd(const float *prop, const int64_t *idx, const float *distsq,
+                              const int32_t *argmax, const float *grad_mean,
+                              const float *grad_max, int64_t n_vert, int32_t K, int32_t P,
+                              float *out_d_prop, float *out_d_distsq, fgc_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FGC_B200_H */

@@ -1,0 +1,125 @@
+"""Generate the committed golden vectors by running the reference's own CPU ops.
+
+    python oracle/build_ref.py && python tests/golden/make_golden.py
+
+Needs oracle/_ref/binned_knn_ops.so (built from the unmodified reference
+sources).  Writes tests/golden/{knn,binning,gravnet,misc}.npz.  The tests only
+read those files; they never need the reference checkout.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, HERE)
+
+import cases  # noqa: E402
+from oracle import ref_ops  # noqa: E402
+from fastgraphcompute_b200 import synthetic  # noqa: E402
+
+
+def run_knn(c):
+    coords = torch.tensor(c["coords"], requires_grad="grad" in c)
+    rs = torch.tensor(c["row_splits"], dtype=torch.int64)
+    kw = {}
+    if "n_bins" in c:
+        kw["n_bins"] = torch.tensor(c["n_bins"], dtype=torch.int64)
+    if "direction" in c:
+        kw["direction"] = torch.tensor(c["direction"], dtype=torch.int64)
+    if "max_bin_dims" in c:
+        kw["max_bin_dims"] = int(c["max_bin_dims"])
+    if c.get("tf_compat"):
+        kw["torch_compatible_indices"] = True
+    idx, dist = ref_ops.ref_binned_select_knn(int(c["K"]), coords, rs, **kw)
+    out = dict(idx=idx.numpy().astype(np.int32), distsq=dist.detach().numpy())
+    if "grad" in c:
+        (dist * torch.tensor(c["grad"])).sum().backward()
+        out["grad_coords"] = coords.grad.numpy()
+    return out
+
+
+def main():
+    torch.set_num_threads(1)
+    store = {}
+    for name, c in cases.knn_cases().items():
+        out = run_knn(c)
+        for k, v in c.items():
+            store[f"{name}/in/{k}"] = np.asarray(v)
+        for k, v in out.items():
+            store[f"{name}/out/{k}"] = v
+        print("knn", name, out["idx"].shape)
+    np.savez_compressed(os.path.join(HERE, "knn.npz"), **store)
+
+    store = {}
+    for name, c in cases.binning_cases().items():
+        kw = {}
+        if "bin_width" in c:
+            kw["bin_width"] = torch.tensor(c["bin_width"])
+        if "n_bins" in c:
+            kw["n_bins"] = torch.tensor(c["n_bins"], dtype=torch.int64)
+        if c.get("pre_normalized"):
+            kw["pre_normalized"] = True
+        r = ref_ops.ref_bin_by_coordinates(torch.tensor(c["coords"]),
+                                           torch.tensor(c["row_splits"], dtype=torch.int64), **kw)
+        for k, v in c.items():
+            store[f"{name}/in/{k}"] = np.asarray(v)
+        for k, v in zip(("bin_indices", "flat", "n_bins", "bin_width", "n_per_bin"), r):
+            store[f"{name}/out/{k}"] = v.numpy()
+        print("binning", name)
+    # the reference's own fixture (tests/test_bbc_data.npy, detector-like coordinates),
+    # binned as its smoke test does (n_bins = 21, one row split)
+    fixture = os.path.join(ref_ops.__dict__.get("_REFERENCE_ROOT", "/root/reference"), "tests", "test_bbc_data.npy")
+    if os.path.exists(fixture):
+        data = np.load(fixture).astype(np.float32)
+        r = ref_ops.ref_bin_by_coordinates(torch.tensor(data), torch.tensor([0, data.shape[0]]),
+                                           n_bins=torch.tensor(21))
+        store["bbc_fixture/in/coords"] = data
+        store["bbc_fixture/in/row_splits"] = np.array([0, data.shape[0]])
+        store["bbc_fixture/in/n_bins"] = np.array(21)
+        for k, v in zip(("bin_indices", "flat", "n_bins", "bin_width", "n_per_bin"), r):
+            store[f"bbc_fixture/out/{k}"] = v.numpy()
+        print("binning bbc_fixture", data.shape)
+    np.savez_compressed(os.path.join(HERE, "binning.npz"), **store)
+
+    store = {}
+    for name, c in cases.gravnet_cases().items():
+        torch.manual_seed(1)
+        m = ref_ops.RefGravNetOp(c["in_channels"], c["out_channels"], c["space"], c["propagate"], c["k"])
+        synthetic.init_gravnet_weights(m, seed=3)
+        g = torch.Generator().manual_seed(5)
+        x = torch.randn((c["n"], c["in_channels"]), generator=g, requires_grad=True)
+        rs = torch.tensor(c["row_splits"], dtype=torch.int32)
+        out, idx, dsq, space = m(x, rs)
+        (out ** 2).sum().backward()
+        store[f"{name}/in/x"] = x.detach().numpy()
+        store[f"{name}/in/row_splits"] = c["row_splits"]
+        for k, v in c.items():
+            if k != "row_splits":
+                store[f"{name}/in/{k}"] = np.asarray(v)
+        for k, v in m.state_dict().items():
+            store[f"{name}/weights/{k}"] = v.numpy()
+        store[f"{name}/out/out"] = out.detach().numpy()
+        store[f"{name}/out/idx"] = idx.numpy().astype(np.int32)
+        store[f"{name}/out/distsq"] = dsq.detach().numpy()
+        store[f"{name}/out/space"] = space.detach().numpy()
+        store[f"{name}/out/grad_x"] = x.grad.numpy()
+        for k, p in m.named_parameters():
+            store[f"{name}/grad/{k}"] = p.grad.numpy()
+        print("gravnet", name)
+    np.savez_compressed(os.path.join(HERE, "gravnet.npz"), **store)
+
+    # index_replacer on random data incl. negative and out-of-range entries
+    rng = np.random.RandomState(34)
+    tbr = rng.randint(-3, 130, size=(40, 7)).astype(np.int64)
+    rpl = rng.permutation(280).astype(np.int64)
+    rep = ref_ops.ref_index_replacer(torch.tensor(tbr), torch.tensor(rpl)).numpy()
+    np.savez_compressed(os.path.join(HERE, "misc.npz"), ir_in=tbr, ir_repl=rpl, ir_out=rep)
+    print("misc done")
+
+
+if __name__ == "__main__":
+    main()
