@@ -1,0 +1,407 @@
+#!/usr/bin/env python
+"""Benchmark of the spatial-graph hot path: binned kNN query points per second.
+
+    python bench.py --gpus N --steps K --warmup W            # this implementation (sm_100a)
+    python bench.py --impl reference --steps K --warmup W     # the reference's CPU path
+
+A step is one forward + backward pass of binned_select_knn over one batch of synthetic
+input: the single-event workload of the headline metric (200 000 points, D = 4, K = 32,
+50-component Gaussian mixture; fastgraphcompute_b200.synthetic.c2_gaussian_mixture).
+With N > 1 every rank (one process per GPU, launched by torch.distributed.run) works on
+its own event of that size -- events are independent, so there is no data-path
+collective -- and the reported value is the whole-job aggregate (weak scaling).
+
+One JSON line is printed by rank 0.  `value` is measured with the inputs resident in
+HBM; `e2e` is measured through the public API from pinned HOST buffers (host->device
+copies of coordinates, row splits and upstream gradient, device->host copies of
+indices, squared distances and coordinate gradients inside the timed region).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "binned_knn_query_points_per_sec_K32_D4"
+UNIT = "points/s"
+WORKLOAD = "c2: single-event binned kNN fwd+bwd, N=200000, D=4, K=32, 50-component Gaussian mixture sigma=0.02"
+L2_FLUSH_BYTES = 256 << 20
+
+# DRAM traffic of one k_knn launch on this workload (dram__bytes_read.sum +
+# dram__bytes_write.sum from an ncu capture, summarised under profiles/); None until captured.
+KNN_KERNEL_DRAM_TRAFFIC_BYTES = None
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples, time-stamped on arrival."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_id):
+        self.samples = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(gpu_id), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "20"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        rows = []
+        for ts, line in self.samples:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                rows.append((ts, float(parts[0]), float(parts[1]), parts[4:8]))
+            except ValueError:
+                continue
+        under = [r for r in rows if t0 <= r[0] <= t1 + 0.05] or rows
+        if not under:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = sorted({names[i] for r in under for i in range(4) if r[3][i].lower() == "active"})
+        return {"sm_mhz": statistics.median(r[1] for r in under), "sm_max_mhz": under[0][2],
+                "reasons": reasons, "samples": len(under)}
+
+
+def gpu_identifier(torch, dev_index):
+    try:
+        u = str(torch.cuda.get_device_properties(dev_index).uuid)
+        return u if u.startswith("GPU-") else "GPU-" + u
+    except Exception:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            return vis.split(",")[dev_index]
+        return str(dev_index)
+
+
+# --------------------------------------------------------------------------- reference arm
+
+def cpu_reference_fwd_bwd(workload, torch):
+    """One forward + backward of the reference's own CPU ops (oracle/_ref) or, where that
+    library is absent, of the C restatement (oracle/).  Returns (seconds, kind)."""
+    from oracle import ref_ops
+    if ref_ops.available():
+        coords = workload.coords.clone().requires_grad_(True)
+        t0 = time.perf_counter()
+        idx, dist = ref_ops.ref_binned_select_knn(workload.K, coords, workload.row_splits)
+        (dist * workload.grad_distsq).sum().backward()
+        return time.perf_counter() - t0, "reference"
+    from oracle import oracle
+    c = workload.coords.numpy()
+    t0 = time.perf_counter()
+    idx, dist = oracle.binned_select_knn(workload.K, c, workload.row_splits.numpy())
+    oracle.binned_select_knn_grad(workload.grad_distsq.numpy(), idx, c)
+    return time.perf_counter() - t0, "port"
+
+
+def run_reference(args):
+    rank = env_int("RANK", 0)
+    if rank != 0:
+        return
+    import torch
+    from fastgraphcompute_b200 import synthetic
+    full = synthetic.c2_gaussian_mixture()
+    # bound the whole run to a few minutes: probe once, then shrink the per-step sample if needed
+    probe = synthetic.c2_gaussian_mixture(scale=0.1)
+    t_probe, kind = cpu_reference_fwd_bwd(probe, torch)
+    est_full = t_probe * 12.0          # cost per point grows with the event size
+    budget = 200.0
+    total_steps = args.steps + args.warmup
+    scale = 1.0
+    if est_full * total_steps > budget:
+        scale = max(0.05, min(1.0, budget / (est_full * total_steps)))
+    w = full if scale == 1.0 else synthetic.c2_gaussian_mixture(scale=scale)
+    for _ in range(args.warmup):
+        cpu_reference_fwd_bwd(w, torch)
+    times = []
+    for _ in range(args.steps):
+        t, kind = cpu_reference_fwd_bwd(w, torch)
+        times.append(t)
+    total = sum(times)
+    value = w.n_points * args.steps / total
+    sample = "%d of %d points per step (same generator, scale %.3g), %d steps" % (
+        w.n_points, full.n_points, scale, args.steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "device": "host CPU", "n_points_per_step": w.n_points},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": 1, "kind": kind, "sample": sample,
+                         "aten_threads": torch.get_num_threads(),
+                         "note": "the reference's kNN, binning and gradient loops are single-threaded"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- this implementation
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    world = env_int("WORLD_SIZE", 1)
+    rank = env_int("RANK", 0)
+    local_rank = env_int("LOCAL_RANK", 0)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this implementation has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import fastgraphcompute_b200 as fgc
+    from fastgraphcompute_b200 import _cabi, synthetic
+    from fastgraphcompute_b200.extensions import binned_select_knn as knn_mod
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    w = synthetic.c2_gaussian_mixture(seed=rank)
+    n, K = w.n_points, w.K
+    h_coords = w.coords.pin_memory()
+    h_rs = w.row_splits.pin_memory()
+    h_grad = w.grad_distsq.pin_memory()
+    d_coords = h_coords.to(dev)
+    d_rs = h_rs.to(dev)
+    d_grad = h_grad.to(dev)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+
+    def step_resident():
+        c = d_coords.detach().requires_grad_(True)
+        idx, dsq = fgc.binned_select_knn(K, c, d_rs)
+        dsq.backward(d_grad)
+        return idx, dsq, c.grad
+
+    sampler = ClockSampler(gpu_identifier(torch, local_rank)) if rank == 0 else None
+
+    # ---- device-resident timing ("value") ----------------------------------------------------
+    search_events = []
+
+    def hook(tag):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        search_events.append((tag, e))
+
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step_resident()
+    barrier()
+    t_load0 = time.time()
+    knn_mod.phase_hook = hook
+    pairs = []
+    for _ in range(args.steps):
+        flush.zero_()                       # evict the 3.2 MB inputs and the outputs from L2
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step_resident()
+        e1.record()
+        pairs.append((e0, e1))
+    knn_mod.phase_hook = None
+    barrier()
+    t_load1 = time.time()
+    step_ms = [a.elapsed_time(b) for a, b in pairs]
+    total_ms = max_over_ranks(sum(step_ms))
+    value = world * n * args.steps / (total_ms * 1e-3)
+    begins = [e for t, e in search_events if t == "search_begin"]
+    ends = [e for t, e in search_events if t == "search_end"]
+    knn_ms = [a.elapsed_time(b) for a, b in zip(begins, ends)]
+    knn_ms_avg = sum(knn_ms) / len(knn_ms)
+
+    # ---- end to end from host buffers ("e2e") --------------------------------------------------
+    o_idx = torch.empty((n, K), dtype=torch.int64).pin_memory()
+    o_dsq = torch.empty((n, K), dtype=torch.float32).pin_memory()
+    o_grad = torch.empty((n, w.coords.shape[1]), dtype=torch.float32).pin_memory()
+
+    def step_e2e():
+        c = h_coords.to(dev, non_blocking=True).requires_grad_(True)
+        rs = h_rs.to(dev, non_blocking=True)
+        g = h_grad.to(dev, non_blocking=True)
+        idx, dsq = fgc.binned_select_knn(K, c, rs)
+        dsq.backward(g)
+        o_idx.copy_(idx, non_blocking=True)
+        o_dsq.copy_(dsq.detach(), non_blocking=True)
+        o_grad.copy_(c.grad, non_blocking=True)
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    pairs = []
+    for _ in range(args.steps):
+        flush.zero_()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step_e2e()
+        e1.record()
+        pairs.append((e0, e1))
+    barrier()
+    e2e_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in pairs))
+    e2e_value = world * n * args.steps / (e2e_ms * 1e-3)
+    h2d = h_coords.numel() * 4 + h_rs.numel() * 8 + h_grad.numel() * 4
+    d2h = o_idx.numel() * 8 + o_dsq.numel() * 4 + o_grad.numel() * 4
+
+    clocks = sampler.summary(t_load0, t_load1) if sampler else None
+    if sampler:
+        sampler.stop()
+
+    # ---- candidate count of the search (for the FP32 view of the roofline) -------------------
+    idx, dsq, ws = knn_mod.knn_forward_raw(d_coords, d_rs, K, None, False, count_evals=True)
+    n_evals, grid_shape, cell_w = knn_mod.read_counters(ws)
+    del idx, dsq, ws
+
+    # ---- GravNet layer (second half of the headline metric) -------------------------------
+    gravnet = None
+    if not args.no_gravnet:
+        from fastgraphcompute_b200.gnn_ops import GravNetOp
+        gw = synthetic.c4_gravnet(seed=rank)
+        m = synthetic.init_gravnet_weights(
+            GravNetOp(gw.in_channels, gw.out_channels, gw.space_dimensions, gw.propagate_dimensions,
+                      gw.k)).to(dev)
+        x = gw.x.to(dev).requires_grad_(True)
+        rs = gw.row_splits.to(dev)
+
+        def gstep():
+            for p in m.parameters():
+                p.grad = None
+            x.grad = None
+            out = m(x, rs)[0]
+            (out ** 2).sum().backward()
+
+        for _ in range(3):
+            gstep()
+        barrier()
+        gp = []
+        for _ in range(5):
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gstep()
+            e1.record()
+            gp.append((e0, e1))
+        barrier()
+        g_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in gp)) / 5
+        gravnet = {"fwd_bwd_ms": g_ms, "n_gpus": world,
+                   "config": "c4: GravNetOp(64->64, space 4, propagate 32, k 40), 16 events x 100000 points per GPU, loss sum(out^2)",
+                   "inputs": "x 410 MB per GPU (larger than L2)", "steps": 5, "warmup": 3}
+        del x, m
+
+    # ---- CPU baseline beside it (rank 0, single-GPU runs only) -----------------------------
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        wb = synthetic.c2_gaussian_mixture(seed=0)
+        t, kind = cpu_reference_fwd_bwd(wb, torch)
+        cpu_baseline = {"value": wb.n_points / t, "unit": UNIT, "cores": 1, "kind": kind,
+                        "sample": "the full workload once (200000 points, fwd+bwd, %.1f s)" % t,
+                        "aten_threads": torch.get_num_threads(),
+                        "note": "the reference's kNN, binning and gradient loops are single-threaded"}
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        d = w.coords.shape[1]
+        alg_bytes = n * (4 * d + 8 * K + 4 * K)          # coords read + int64 idx + fp32 distsq written
+        achieved = alg_bytes / (knn_ms_avg * 1e-3) / 1e9
+        launches_per_step = _cabi.KERNELS_BUILD_GRID + _cabi.KERNELS_SEARCH + _cabi.KERNELS_KNN_BWD
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "points_per_gpu": n, "sharding": "one event per GPU, no data-path collective",
+                       "l2": "flushed between steps by a 256 MiB write outside the timed events (inputs are 3.2 MB)",
+                       "timing": "CUDA events per step on the launching stream, summed; max over ranks"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "k_knn (neighbour search)", "achieved": achieved,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": "of " + peak_kind, "traffic": KNN_KERNEL_DRAM_TRAFFIC_BYTES,
+                         "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": knn_ms_avg},
+            "roofline_fp32": {"note": "the search is bound by CUDA-core issue, not by HBM: distance evaluations x 3*D flops",
+                              "distance_evals_per_launch": n_evals, "evals_per_query": n_evals / n,
+                              "achieved_tflops": n_evals * 3 * d / (knn_ms_avg * 1e-3) / 1e12,
+                              "grid_shape": grid_shape, "cell_width": cell_w},
+            "clocks": clocks,
+        }
+        if cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline
+        if gravnet:
+            line["gravnet"] = gravnet
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-gravnet", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

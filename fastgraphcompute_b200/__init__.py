@@ -5,7 +5,7 @@ hot path behind the reference's Python entry points (fastgraphcompute/__init__.p
     from fastgraphcompute_b200.gnn_ops import GravNetOp
 
 CUDA tensors only; the CUDA library libfgc_b200.so must have been built
-(python -m fastgraphcompute_b200.build).
+(python fastgraphcompute_b200/build.py).
 """
 from .extensions.bin_by_coordinates import bin_by_coordinates
 from .extensions.binned_select_knn import binned_select_knn

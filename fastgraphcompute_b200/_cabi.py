@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libfgc_b200.so")
 if not os.path.exists(LIB_PATH):
     raise RuntimeError(
         "fastgraphcompute_b200: %s is missing. Build it with "
-        "`python -m fastgraphcompute_b200.build` (needs nvcc; targets sm_100a). "
+        "`python fastgraphcompute_b200/build.py` (needs nvcc; targets sm_100a). "
         "There is no fallback implementation." % LIB_PATH)
 
 lib = ctypes.CDLL(LIB_PATH)
@@ -28,6 +28,13 @@ c_float = ctypes.c_float
 
 FGC_MAX_BIN_DIMS = 8
 FGC_MAX_K = 257
+
+# kernels launched per call (for launch accounting in benchmarks)
+KERNELS_BUILD_GRID = 8
+KERNELS_SEARCH = 1
+KERNELS_KNN_BWD = 1
+KERNELS_GRAVNET_FWD = 1
+KERNELS_GRAVNET_BWD = 1
 
 STATUS_NONFINITE = 1
 STATUS_BAD_ROW_SPLITS = 2
@@ -68,6 +75,13 @@ SIGNATURES = {
     "fgc_binned_knn_fwd": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_void_p, c_i64, c_i32, c_void_p,
                                           c_i32, c_float, c_void_p, c_void_p, c_void_p, c_size,
                                           c_void_p]),
+    "fgc_knn_build_grid": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_void_p, c_i64, c_i32, c_void_p,
+                                          c_float, c_void_p, c_size, c_void_p]),
+    "fgc_knn_search": (ctypes.c_int, [c_i64, c_i32, c_i64, c_i32, c_i32, c_i32, c_i32, c_void_p,
+                                      c_void_p, c_void_p, c_size, c_void_p]),
+    "fgc_knn_read_counters": (ctypes.c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint64),
+                                             ctypes.POINTER(c_i32), ctypes.POINTER(c_float),
+                                             c_void_p]),
     "fgc_read_status": (ctypes.c_int, [c_void_p, ctypes.POINTER(c_i32), c_void_p]),
     "fgc_binned_knn_bwd": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i32, c_i32,
                                           c_void_p, c_void_p]),

@@ -1,6 +1,8 @@
 """Build recipe of libfgc_b200.so: nvcc, sm_100a only, in-tree output.
 
-    python -m fastgraphcompute_b200.build [--force]
+    python fastgraphcompute_b200/build.py [--force] [-v]
+
+(run as a script: it must work while the package itself cannot be imported yet)
 
 The shared object has no PyTorch dependency; the Python layer loads it with
 ctypes and hands it raw device pointers and the current CUDA stream.

@@ -638,27 +638,38 @@ extern "C" int fgc_read_status(const void *workspace_or_params, int32_t *status_
     return FGC_OK;
 }
 
-extern "C" int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,
-                                  const int64_t *row_splits, int64_t n_rs, int32_t K,
-                                  const int64_t *direction_or_null, int32_t tf_compat,
-                                  float target_occupancy, int64_t *out_idx, float *out_distsq,
-                                  void *workspace, size_t workspace_bytes, fgc_stream_t stream)
+namespace fgc {
+
+static int check_knn_args(int64_t n_vert, int32_t n_coords, const int64_t *row_splits, int64_t n_rs,
+                          int32_t K, const void *workspace, size_t workspace_bytes, KnnWorkspace *L)
 {
-    using namespace fgc;
     if (n_vert < 0 || n_rs < 1 || !row_splits) return FGC_ERR_BAD_ARGUMENT;
     if (n_vert > 0x7fffffff || n_rs > 0x7fffffff) return FGC_ERR_TOO_LARGE;
     if (n_coords < 2) return n_coords < 1 ? FGC_ERR_BAD_ARGUMENT : FGC_ERR_UNSUPPORTED_DIM;
     if (n_coords > 8) return FGC_ERR_UNSUPPORTED_DIM;
     if (K < 1 || K > FGC_MAX_K) return FGC_ERR_UNSUPPORTED_K;
-    const KnnWorkspace L = knn_workspace_layout(n_vert, n_coords, n_rs, K);
-    if (!workspace || workspace_bytes < L.total || ((uintptr_t)workspace & 255)) return FGC_ERR_WORKSPACE;
+    *L = knn_workspace_layout(n_vert, n_coords, n_rs, K);
+    if (!workspace || workspace_bytes < L->total || ((uintptr_t)workspace & 255)) return FGC_ERR_WORKSPACE;
+    return FGC_OK;
+}
+
+}  // namespace fgc
+
+extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n_coords,
+                                  const int64_t *row_splits, int64_t n_rs, int32_t K,
+                                  const int64_t *direction_or_null, float target_occupancy,
+                                  void *workspace, size_t workspace_bytes, fgc_stream_t stream)
+{
+    using namespace fgc;
+    KnnWorkspace L;
+    const int rc = check_knn_args(n_vert, n_coords, row_splits, n_rs, K, workspace, workspace_bytes, &L);
+    if (rc != FGC_OK) return rc;
     cudaStream_t s = (cudaStream_t)stream;
     char *ws = (char *)workspace;
     KnnGrid *grid = (KnnGrid *)(ws + L.header);
     FGC_RETURN_IF_CUDA(cudaMemsetAsync(grid, 0, kGridHeaderBytes, s));
     if (n_vert == 0) return FGC_OK;
-    if (!coords || !out_idx || !out_distsq) return FGC_ERR_BAD_ARGUMENT;
-    if (n_rs < 2) return FGC_ERR_BAD_ARGUMENT;
+    if (!coords || n_rs < 2) return FGC_ERR_BAD_ARGUMENT;
 
     int *counts = (int *)(ws + L.counts);
     int *blocksums = (int *)(ws + L.blocksums);
@@ -669,26 +680,24 @@ extern "C" int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n
     uint8_t *sflag = (uint8_t *)(ws + L.sflag);
     float4 *scoords = (float4 *)(ws + L.scoords);
 
-    const int nv = L.nv;
     const int n = (int)n_vert;
     const int n_events = (int)n_rs - 1;
     const int n_bin_dims = n_coords < 3 ? n_coords : 3;
     if (!(target_occupancy > 0.f)) target_occupancy = 2.0f;
     const int64_t bins_cap64 = L.cap_bins / n_events;
     const int bins_cap = (int)(bins_cap64 < 1 ? 1 : bins_cap64);
-    double bt = (double)n_vert / (double)n_events / (double)target_occupancy;
+    const double bt = (double)n_vert / (double)n_events / (double)target_occupancy;
     int bins_target = bt >= (double)bins_cap ? bins_cap : (int)(bt + 0.5);
     if (bins_target < 1) bins_target = 1;
 
     const int pt_blocks = (n + 255) / 256;
-    int red_blocks = pt_blocks < 148 * 4 ? pt_blocks : 148 * 4;
+    const int red_blocks = pt_blocks < 148 * 4 ? pt_blocks : 148 * 4;
     k_minmax<<<red_blocks, 256, 0, s>>>(coords, n, n_coords, n_bin_dims, grid);
     FGC_CHECK_LAUNCH();
     k_grid_setup<<<1, 32, 0, s>>>(grid, row_splits, (int)n_rs, n, n_bin_dims, bins_target, bins_cap);
     FGC_CHECK_LAUNCH();
-    // the cell count is only known on the device: size these grids for the
-    // requested table (bins_target is what k_grid_setup aims for, the shape can
-    // overshoot it up to bins_cap) and let surplus blocks return at once.
+    // The cell count is only known on the device: the scan grids are sized for the
+    // largest table k_grid_setup may choose and surplus blocks return at once.
     const int64_t max_entries = (int64_t)bins_cap * n_events + 1;
     const int scan_blocks = (int)ceil_div64(max_entries, kScanTile);
     k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid);
@@ -702,18 +711,69 @@ extern "C" int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n
     FGC_CHECK_LAUNCH();
     k_scan_apply<<<scan_blocks, 256, 0, s>>>(counts, grid, blocksums);
     FGC_CHECK_LAUNCH();
-    k_scatter<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, nv, direction_or_null, grid, counts, pbin,
-                                        prank, scoords, sorig, sbin, sflag);
+    k_scatter<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, L.nv, direction_or_null, grid, counts,
+                                        pbin, prank, scoords, sorig, sbin, sflag);
     FGC_CHECK_LAUNCH();
+    return FGC_OK;
+}
 
+extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
+                              int32_t has_direction, int32_t tf_compat, int32_t count_evals,
+                              int64_t *out_idx, float *out_distsq, void *workspace,
+                              size_t workspace_bytes, fgc_stream_t stream)
+{
+    using namespace fgc;
+    KnnWorkspace L;
+    static const int64_t dummy_rs = 0;
+    const int rc = check_knn_args(n_vert, n_coords, &dummy_rs, n_rs, K, workspace, workspace_bytes, &L);
+    if (rc != FGC_OK) return rc;
+    if (n_vert == 0) return FGC_OK;
+    if (!out_idx || !out_distsq) return FGC_ERR_BAD_ARGUMENT;
+    char *ws = (char *)workspace;
     KnnArgs a;
-    a.scoords = scoords; a.sorig = sorig; a.sbin = sbin;
-    a.sflag = direction_or_null ? sflag : nullptr;
-    a.bounds = counts; a.grid = grid;
-    a.out_idx = out_idx; a.out_dist = out_distsq;
-    a.n_vert = n; a.K = K; a.n_coords = n_coords; a.tf_compat = tf_compat;
-    a.count_evals = 0;
-    int rc = nv == 1 ? launch_knn_nv<1>(a, s) : launch_knn_nv<2>(a, s);
-    if (rc != 0) return rc;
+    a.scoords = (const float4 *)(ws + L.scoords);
+    a.sorig = (const int *)(ws + L.sorig);
+    a.sbin = (const int *)(ws + L.sbin);
+    a.sflag = has_direction ? (const uint8_t *)(ws + L.sflag) : nullptr;
+    a.bounds = (const int *)(ws + L.counts);
+    a.grid = (const KnnGrid *)(ws + L.header);
+    a.out_idx = out_idx;
+    a.out_dist = out_distsq;
+    a.n_vert = (int)n_vert;
+    a.K = K;
+    a.n_coords = n_coords;
+    a.tf_compat = tf_compat;
+    a.count_evals = count_evals;
+    const int lrc = L.nv == 1 ? launch_knn_nv<1>(a, (cudaStream_t)stream)
+                              : launch_knn_nv<2>(a, (cudaStream_t)stream);
+    return lrc;
+}
+
+extern "C" int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,
+                                  const int64_t *row_splits, int64_t n_rs, int32_t K,
+                                  const int64_t *direction_or_null, int32_t tf_compat,
+                                  float target_occupancy, int64_t *out_idx, float *out_distsq,
+                                  void *workspace, size_t workspace_bytes, fgc_stream_t stream)
+{
+    int rc = fgc_knn_build_grid(coords, n_vert, n_coords, row_splits, n_rs, K, direction_or_null,
+                                target_occupancy, workspace, workspace_bytes, stream);
+    if (rc != FGC_OK) return rc;
+    return fgc_knn_search(n_vert, n_coords, n_rs, K, direction_or_null != nullptr, tf_compat, 0,
+                          out_idx, out_distsq, workspace, workspace_bytes, stream);
+}
+
+extern "C" int fgc_knn_read_counters(const void *workspace, uint64_t *n_evals_host,
+                                     int32_t *grid_shape_host, float *cell_width_host,
+                                     fgc_stream_t stream)
+{
+    using namespace fgc;
+    if (!workspace) return FGC_ERR_BAD_ARGUMENT;
+    KnnGrid h;
+    cudaStream_t s = (cudaStream_t)stream;
+    FGC_RETURN_IF_CUDA(cudaMemcpyAsync(&h, workspace, sizeof(KnnGrid), cudaMemcpyDeviceToHost, s));
+    FGC_RETURN_IF_CUDA(cudaStreamSynchronize(s));
+    if (n_evals_host) *n_evals_host = h.n_evals;
+    if (grid_shape_host) { grid_shape_host[0] = h.n[0]; grid_shape_host[1] = h.n[1]; grid_shape_host[2] = h.n[2]; }
+    if (cell_width_host) *cell_width_host = h.w;
     return FGC_OK;
 }

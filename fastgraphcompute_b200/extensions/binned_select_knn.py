@@ -32,13 +32,20 @@ def _raise_for_status(status):
         raise RuntimeError("binned_select_knn: internal error, status %d" % status)
 
 
-def knn_forward_raw(coords, row_splits, K, direction, tf_compat):
-    """Launch fgc_binned_knn_fwd on prepared tensors; returns (idx, distsq, workspace)."""
+# Optional instrumentation: a callable(tag) invoked on the launching stream right before and
+# after the search kernel ("search_begin" / "search_end"); benchmarks record CUDA events here.
+phase_hook = None
+
+
+def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=False):
+    """Launch the forward (fgc_knn_build_grid + fgc_knn_search, which is what
+    fgc_binned_knn_fwd does) on prepared tensors; returns (idx, distsq, workspace)."""
     dev = coords.device
     n_vert, n_coords = coords.shape
+    n_rs = row_splits.numel()
     idx = torch.empty((n_vert, K), dtype=torch.int64, device=dev)
     dist = torch.empty((n_vert, K), dtype=torch.float32, device=dev)
-    nbytes = _cabi.lib.fgc_knn_workspace_bytes(n_vert, n_coords, row_splits.numel(), K)
+    nbytes = _cabi.lib.fgc_knn_workspace_bytes(n_vert, n_coords, n_rs, K)
     if nbytes == 0:
         if K < 1 or K > _cabi.FGC_MAX_K:
             raise ValueError("binned_select_knn: K must be in 1..%d, got %d" % (_cabi.FGC_MAX_K, K))
@@ -46,16 +53,36 @@ def knn_forward_raw(coords, row_splits, K, direction, tf_compat):
     ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         stream = _cabi.current_stream(dev)
-        _cabi.check(_cabi.lib.fgc_binned_knn_fwd(
-            _cabi.ptr(coords), n_vert, n_coords, _cabi.ptr(row_splits), row_splits.numel(), K,
-            _cabi.ptr(direction), int(bool(tf_compat)), float(target_occupancy), _cabi.ptr(idx),
-            _cabi.ptr(dist), _cabi.ptr(ws), nbytes, stream), "fgc_binned_knn_fwd")
+        _cabi.check(_cabi.lib.fgc_knn_build_grid(
+            _cabi.ptr(coords), n_vert, n_coords, _cabi.ptr(row_splits), n_rs, K,
+            _cabi.ptr(direction), float(target_occupancy), _cabi.ptr(ws), nbytes, stream),
+            "fgc_knn_build_grid")
+        if phase_hook is not None:
+            phase_hook("search_begin")
+        _cabi.check(_cabi.lib.fgc_knn_search(
+            n_vert, n_coords, n_rs, K, int(direction is not None), int(bool(tf_compat)),
+            int(bool(count_evals)), _cabi.ptr(idx), _cabi.ptr(dist), _cabi.ptr(ws), nbytes, stream),
+            "fgc_knn_search")
+        if phase_hook is not None:
+            phase_hook("search_end")
         if check_status:
             st = ctypes.c_int32(0)
             _cabi.check(_cabi.lib.fgc_read_status(_cabi.ptr(ws), ctypes.byref(st), stream),
                         "fgc_read_status")
             _raise_for_status(st.value)
     return idx, dist, ws
+
+
+def read_counters(ws):
+    """(distance evaluations, grid shape [3], cell width) of a forward's workspace."""
+    n_evals = ctypes.c_uint64(0)
+    shape = (ctypes.c_int32 * 3)()
+    width = ctypes.c_float(0)
+    with torch.cuda.device(ws.device):
+        _cabi.check(_cabi.lib.fgc_knn_read_counters(
+            _cabi.ptr(ws), ctypes.byref(n_evals), shape, ctypes.byref(width),
+            _cabi.current_stream(ws.device)), "fgc_knn_read_counters")
+    return n_evals.value, [shape[0], shape[1], shape[2]], width.value
 
 
 class _BinnedKNN(torch.autograd.Function):

@@ -139,6 +139,40 @@ int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,
                        void *workspace, size_t workspace_bytes, fgc_stream_t stream);
 
 /*
+ * The two halves of fgc_binned_knn_fwd, for callers that search the same grid more
+ * than once or want to time the phases separately.
+ *
+ * fgc_knn_build_grid: everything up to the search (extent reduction, grid choice,
+ * histogram, scan, counting-sort scatter).  Replaces steps 2-8 of
+ * BinnedKNNAutograd::forward (extensions/binned_knn_autograd_kernel.cpp:100-145:
+ * calculate_optimal_bins, bin_by_coordinates, argsort, index_select, cumsum).
+ *
+ * fgc_knn_search: the neighbour search proper on a built workspace, including the
+ * mapping back to original ids and row order.  Replaces binned_select_knn_cuda_fn
+ * (extensions/binned_select_knn_cuda_kernel.cu:252-384) + index_replacer + un-sort
+ * scatter (extensions/binned_knn_autograd_kernel.cpp:157-195).  has_direction must say
+ * whether the grid was built with a direction array.  count_evals != 0 adds the number of
+ * distance evaluations to a counter in the workspace (fgc_knn_read_counters).
+ */
+int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n_coords,
+                       const int64_t *row_splits, int64_t n_rs, int32_t K,
+                       const int64_t *direction_or_null, float target_occupancy,
+                       void *workspace, size_t workspace_bytes, fgc_stream_t stream);
+int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
+                   int32_t has_direction, int32_t tf_compat, int32_t count_evals,
+                   int64_t *out_idx, float *out_distsq, void *workspace,
+                   size_t workspace_bytes, fgc_stream_t stream);
+
+/*
+ * Diagnostics of a built workspace, copied to the host (synchronises the stream): the
+ * distance-evaluation counter, the grid shape [3] and the cell width.  Any output pointer
+ * may be NULL.  No counterpart in the reference.
+ */
+int fgc_knn_read_counters(const void *workspace, uint64_t *n_evals_host,
+                          int32_t *grid_shape_host, float *cell_width_host,
+                          fgc_stream_t stream);
+
+/*
  * Copies the status word at the start of a workspace / fgc_bin_params to the
  * host and waits for the stream (the only synchronising call of the library).
  */

@@ -37,8 +37,12 @@ def run_knn(c):
     idx, dist = ref_ops.ref_binned_select_knn(int(c["K"]), coords, rs, **kw)
     out = dict(idx=idx.numpy().astype(np.int32), distsq=dist.detach().numpy())
     if "grad" in c:
-        (dist * torch.tensor(c["grad"])).sum().backward()
+        # slot-order independent loss: weights apply to the row sorted by distance
+        dist.retain_grad()
+        sorted_d, _ = torch.sort(dist, dim=1, stable=True)
+        (sorted_d * torch.tensor(c["grad"])).sum().backward()
         out["grad_coords"] = coords.grad.numpy()
+        out["grad_dist_slots"] = dist.grad.numpy()   # the same weights in the reference's slot order
     return out
 
 

@@ -109,7 +109,7 @@ def test_knn_golden(golden_dir):
         assert st["max_rel"] == 0.0, name
         if "grad" in i:
             # gradient oracle on the reference's own slot order: bit-identical
-            g = oracle.binned_select_knn_grad(i["grad"], ref_idx, i["coords"])
+            g = oracle.binned_select_knn_grad(c["out"]["grad_dist_slots"], ref_idx, i["coords"])
             assert np.array_equal(g, c["out"]["grad_coords"]), name
 
 
