@@ -198,7 +198,8 @@ def run_b200(args):
 
     import fastgraphcompute_b200 as fgc
     from fastgraphcompute_b200 import _cabi, synthetic
-    from fastgraphcompute_b200.extensions import binned_select_knn as knn_mod
+    import importlib
+    knn_mod = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
 
     def barrier():
         if world > 1:

@@ -77,15 +77,17 @@ def assert_knn_parity(idx, dist, ref_idx, ref_dist, pad_self=False, what=""):
     return dict(rows=n, tie_rows=tie_rows, max_rel=max_rel)
 
 
-def assert_grad_close(a, b, rtol=GRAD_RTOL, what=""):
-    """|a-b| <= rtol * (|b| + scale) elementwise, scale = RMS of b (floating-point sums in a
-    different order cannot be compared element-relative where terms cancel)."""
+def assert_grad_close(a, b, rtol=GRAD_RTOL, what="", scale=None):
+    """|a-b| <= rtol * (|b| + scale) elementwise, scale = RMS of b unless given (floating-point
+    sums in a different order cannot be compared element-relative where terms cancel; pass the
+    magnitude of the summed terms as `scale` for a quantity that is analytically ~0)."""
     a = np.asarray(a, np.float64)
     b = np.asarray(b, np.float64)
     assert a.shape == b.shape, what + " shape mismatch"
     if b.size == 0:
         return 0.0
-    scale = float(np.sqrt(np.mean(b * b)))
+    if scale is None:
+        scale = float(np.sqrt(np.mean(b * b)))
     err = np.abs(a - b) / (np.abs(b) + scale + 1e-30)
     m = float(err.max())
     assert m <= rtol, "%s: max scaled error %g > %g" % (what, m, rtol)

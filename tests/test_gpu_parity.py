@@ -132,7 +132,8 @@ def test_knn_golden(golden_dir):
         tf = "tf_compat" in i and bool(i["tf_compat"])
         st = parity.assert_knn_parity(idx.cpu().numpy(), dist.detach().cpu().numpy(),
                                       c["out"]["idx"], c["out"]["distsq"], pad_self=tf, what=name)
-        ties += st["tie_rows"]
+        if "lattice" not in name and "duplicates" not in name:
+            ties += st["tie_rows"]      # exact ties are expected only in the constructed cases
         if "grad" in i:
             # the golden loss weights the row sorted by distance (slot order carries no meaning)
             sorted_d, _ = torch.sort(dist, dim=1, stable=True)
@@ -296,7 +297,11 @@ def test_gravnet_module_golden(golden_dir):
         (out ** 2).sum().backward()
         parity.assert_grad_close(x.grad.cpu().numpy(), c["out"]["grad_x"], 2e-5, name + " grad_x")
         for k, p in m.named_parameters():
-            parity.assert_grad_close(p.grad.cpu().numpy(), c["grad"][k], 2e-5, name + " grad " + k)
+            # a bias gradient can cancel to ~0 (translating all learned coordinates changes no
+            # distance): measure its error against the scale of the layer's weight gradient
+            wk = k.replace(".bias", ".weight")
+            scale = float(np.sqrt(np.mean(c["grad"][wk].astype(np.float64) ** 2)))
+            parity.assert_grad_close(p.grad.cpu().numpy(), c["grad"][k], 2e-5, name + " grad " + k, scale=scale)
 
 
 def test_gravnet_shape_sweep():
