@@ -304,7 +304,8 @@ def run_b200(args):
 
     # ---- candidate count of the search (for the FP32 view of the roofline) -------------------
     idx, dsq, ws = knn_mod.knn_forward_raw(d_coords, d_rs, K, None, False, count_evals=True)
-    n_evals, grid_shape, cell_w = knn_mod.read_counters(ws)
+    counters, grid_shape, cell_w = knn_mod.read_counters(ws)
+    n_evals = counters[0]
     del idx, dsq, ws
 
     # ---- GravNet layer (second half of the headline metric) -------------------------------

@@ -10,7 +10,7 @@ import os
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libfgc_b200.so")
+LIB_PATH = os.environ.get("FGC_B200_LIB") or os.path.join(_PKG_DIR, "libfgc_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise RuntimeError(

@@ -1,0 +1,426 @@
+// binned_select_knn forward for sm_100a, part 1: the search grid (this file) --
+// part 2, the search itself, is knn_search.cu.
+//
+// Pipeline (all on the caller's stream, no host synchronisation):
+//   k_minmax      fused finite check + min/max of the binned coordinates
+//   k_grid_setup  cell width / grid shape from the extents and the point count
+//   k_zero_counts clear the cell table
+//   k_histogram   cell id per point, warp-aggregated atomic histogram; the value
+//                 returned by the atomic is the point's rank inside its cell
+//   k_scan_*      exclusive scan of the histogram -> cell boundaries
+//   k_scatter     counting-sort scatter: coordinates (padded to float4), original
+//                 id, cell id and direction flag in cell order
+//   k_knn         one warp per query point: walks the neighbouring cells in
+//                 expanding Chebyshev shells, evaluates 32 candidates per step
+//                 (one per lane, 16-byte loads), keeps the K-1 best in registers
+//                 and writes the row at its ORIGINAL position with ORIGINAL ids.
+//
+// What is computed is what the reference's CPU path computes
+// (extensions/binned_knn_autograd_kernel.cpp:85-209 with
+// extensions/binned_select_knn_cpu.cpp:56-208): per row split, the K-1 nearest
+// other points (strict "<" replacement of the current worst, so among equal
+// distances the first one visited stays), squared distances accumulated over the
+// dimensions in order with one rounding per operation.  The visiting order, the
+// grid and the stopping rule are this library's own; they never change which
+// points are nearest, only which of several equidistant points is kept.
+#include "knn_grid.cuh"
+
+namespace fgc {
+
+// ---------------------------------------------------------------------------
+// grid construction
+// ---------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256)
+k_minmax(const float *__restrict__ coords, int n_vert, int n_coords, int n_bin_dims, KnnGrid *g)
+{
+    uint32_t lmin[3] = {0, 0, 0}, lmax[3] = {0, 0, 0};
+    uint32_t bad = 0;
+    for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vert; v += gridDim.x * blockDim.x) {
+        const float *row = coords + (size_t)v * n_coords;
+        for (int c = 0; c < n_coords; c++) {
+            const float x = __ldg(row + c);
+            if (!is_finite_bits(x)) bad = 1;
+            if (c < n_bin_dims) {
+                const uint32_t k = float_to_ordered(x);
+#pragma unroll
+                for (int cc = 0; cc < 3; cc++)
+                    if (cc == c) { lmin[cc] = max(lmin[cc], ~k); lmax[cc] = max(lmax[cc], k); }
+            }
+        }
+    }
+    __shared__ uint32_t s_min[3], s_max[3], s_bad;
+    if (threadIdx.x < 3) { s_min[threadIdx.x] = 0; s_max[threadIdx.x] = 0; }
+    if (threadIdx.x == 0) s_bad = 0;
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < 3; c++) {
+        const uint32_t a = __reduce_max_sync(FGC_FULL_MASK, lmin[c]);
+        const uint32_t b = __reduce_max_sync(FGC_FULL_MASK, lmax[c]);
+        if ((threadIdx.x & 31) == 0) { atomicMax(&s_min[c], a); atomicMax(&s_max[c], b); }
+    }
+    if (__any_sync(FGC_FULL_MASK, bad) && (threadIdx.x & 31) == 0) atomicOr(&s_bad, 1u);
+    __syncthreads();
+    if (threadIdx.x < 3) {
+        atomicMax(&g->min_key[threadIdx.x], s_min[threadIdx.x]);
+        atomicMax(&g->max_key[threadIdx.x], s_max[threadIdx.x]);
+    }
+    if (threadIdx.x == 0 && s_bad) atomicOr(&g->nonfinite, 1u);
+}
+
+// One thread.  Chooses the cell width so that a row split of average size gets
+// about bins_target cells, bounded by bins_cap cells per row split.
+__global__ void __launch_bounds__(32)
+k_grid_setup(KnnGrid *g, int32_t *__restrict__ shelltab, const int64_t *__restrict__ row_splits,
+             int n_rs, int n_vert, int n_bin_dims, int bins_target, int bins_cap)
+{
+    const int lane = threadIdx.x;
+    // shell item table for radii 0..kShellTableMaxD (all lanes)
+    for (int d = 0; d <= kShellTableMaxD; d++)
+        for (int u = lane; u < shell_items(d); u += 32) {
+            int o0, o1, zlo, zhi;
+            shell_item_decode(d, u, o0, o1, zlo, zhi);
+            shelltab[shell_table_offset(d) + u] =
+                (o0 & 0xff) | ((o1 & 0xff) << 8) | ((zlo & 0xff) << 16) | ((zhi & 0xff) << 24);
+        }
+    // row_splits must start at 0, end at n_vert and never decrease (all lanes)
+    int bad_rs = 0;
+    for (int i = 1 + lane; i < n_rs; i += 32)
+        if (row_splits[i] < row_splits[i - 1]) bad_rs = 1;
+    bad_rs = __any_sync(FGC_FULL_MASK, bad_rs);
+    if (lane != 0) return;
+    int status = 0;
+    if (g->nonfinite) status |= FGC_STATUS_NONFINITE;
+    if (bad_rs || row_splits[0] != 0 || row_splits[n_rs - 1] != (int64_t)n_vert)
+        status |= FGC_STATUS_BAD_ROW_SPLITS;
+    const int n_events = n_rs - 1;
+    const int sh = 3 - n_bin_dims;
+    float ext[3];
+    double vol = 1.0;
+    int nz = 0;
+    float ext_max = 0.f;
+    for (int gd = 0; gd < 3; gd++) {
+        if (gd < sh || (status & FGC_STATUS_NONFINITE)) {
+            g->cdim[gd] = gd < sh ? -1 : gd - sh;
+            g->origin[gd] = 0.f;
+            ext[gd] = 0.f;
+        } else {
+            const int c = gd - sh;
+            const float lo = ordered_to_float(~g->min_key[c]);
+            const float hi = ordered_to_float(g->max_key[c]);
+            g->cdim[gd] = c;
+            g->origin[gd] = lo;
+            ext[gd] = __fsub_rn(hi, lo);
+            if (!(ext[gd] >= 0.f) || !is_finite_bits(ext[gd])) ext[gd] = 0.f;
+        }
+        if (ext[gd] > 0.f) { vol *= (double)ext[gd]; nz++; }
+        ext_max = fmaxf(ext_max, ext[gd]);
+    }
+    int n[3] = {1, 1, 1};
+    float w = 1.f;
+    if (nz > 0) {
+        if (bins_target < 1) bins_target = 1;
+        double wd = pow(vol / (double)bins_target, 1.0 / (double)nz);
+        // a degenerate extent ratio can make the width underflow: keep it representable
+        if (!(wd > (double)ext_max * 1e-6)) wd = (double)ext_max * 1e-6;
+        for (int iter = 0; iter < 400; iter++) {
+            w = (float)wd;
+            const float inv = __fdiv_rn(1.0f, w);
+            double prod = 1.0;
+            for (int gd = 0; gd < 3; gd++) {
+                n[gd] = ext[gd] > 0.f ? (int)floorf(__fmul_rn(ext[gd], inv)) + 1 : 1;
+                prod *= (double)n[gd];
+            }
+            if (prod <= (double)bins_cap) break;
+            wd *= 1.05;
+        }
+    }
+    long long B = (long long)n[0] * n[1] * n[2];
+    if (B > bins_cap) {  // cannot happen after the loop above unless the extents are absurd
+        n[0] = n[1] = n[2] = 1; B = 1; w = fmaxf(ext_max, 1.f) * 2.f;
+        status |= FGC_STATUS_INTERNAL;
+    }
+    g->n[0] = n[0]; g->n[1] = n[1]; g->n[2] = n[2];
+    g->B = (int)B;
+    g->n_events = n_events;
+    g->total_bins = (int)(B * n_events);
+    g->w = w;
+    g->inv_w = __fdiv_rn(1.0f, w);
+    g->slack = 4e-6f * fmaxf(ext_max, w);
+    g->status = status;
+}
+
+__global__ void __launch_bounds__(256) k_zero_counts(int *__restrict__ counts, const KnnGrid *g)
+{
+    const int n = g->total_bins + 1;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        counts[i] = 0;
+}
+
+// Cell coordinate of a shifted coordinate; identical in every kernel that needs it.
+__device__ __forceinline__ int cell_of(float x, float origin, float inv_w, int n)
+{
+    const float t = __fsub_rn(x, origin);
+    int b = (int)floorf(__fmul_rn(t, inv_w));
+    b = b < 0 ? 0 : b;
+    return b >= n ? n - 1 : b;
+}
+
+__global__ void __launch_bounds__(256)
+k_histogram(const float *__restrict__ coords, int n_vert, int n_coords,
+            const int64_t *__restrict__ row_splits, int n_rs, const KnnGrid *__restrict__ g,
+            int *__restrict__ counts, int *__restrict__ pbin, int *__restrict__ prank)
+{
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = v < n_vert && g->status == 0;
+    int flat = 0;
+    if (live) {
+        const float *row = coords + (size_t)v * n_coords;
+        int b[3];
+#pragma unroll
+        for (int gd = 0; gd < 3; gd++) {
+            const int c = g->cdim[gd];
+            b[gd] = c < 0 ? 0 : cell_of(__ldg(row + c), g->origin[gd], g->inv_w, g->n[gd]);
+        }
+        const int e = row_split_of(row_splits, n_rs, v);
+        flat = e * g->B + (b[0] * g->n[1] + b[1]) * g->n[2] + b[2];
+    }
+    const unsigned active = __ballot_sync(FGC_FULL_MASK, live);
+    if (live) {
+        // warp-aggregated: one atomic per distinct cell in the warp
+        const unsigned peers = __match_any_sync(active, flat);
+        const int leader = __ffs(peers) - 1;
+        int base = 0;
+        if ((int)(threadIdx.x & 31) == leader) base = atomicAdd(counts + flat, __popc(peers));
+        base = __shfl_sync(peers, base, leader);
+        pbin[v] = flat;
+        prank[v] = base + __popc(peers & lanemask_lt());
+    }
+}
+
+// --- exclusive scan of counts[0 .. total_bins] in place (three kernels) -------
+
+__global__ void __launch_bounds__(256)
+k_scan_tile_sums(const int *__restrict__ counts, const KnnGrid *__restrict__ g,
+                 int *__restrict__ blocksums)
+{
+    const int n = g->total_bins + 1;
+    const int base = blockIdx.x * kScanTile;
+    if (base >= n) return;
+    int s = 0;
+#pragma unroll
+    for (int k = 0; k < kScanTile / 256; k++) {
+        const int i = base + k * 256 + threadIdx.x;
+        if (i < n) s += counts[i];
+    }
+    __shared__ int ws[8];
+    s = __reduce_add_sync(FGC_FULL_MASK, s);
+    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int k = 0; k < 8; k++) t += ws[k];
+        blocksums[blockIdx.x] = t;
+    }
+}
+
+// Single block: exclusive scan of the tile sums.
+__global__ void __launch_bounds__(1024)
+k_scan_block_sums(int *__restrict__ blocksums, const KnnGrid *__restrict__ g)
+{
+    const int n = (g->total_bins + 1 + kScanTile - 1) / kScanTile;
+    __shared__ int ws[32];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int base = 0; base < n; base += 1024) {
+        const int i = base + threadIdx.x;
+        const int x = i < n ? blocksums[i] : 0;
+        int incl = x;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(FGC_FULL_MASK, incl, o);
+            if ((threadIdx.x & 31) >= o) incl += t;
+        }
+        if ((threadIdx.x & 31) == 31) ws[threadIdx.x >> 5] = incl;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            int y = ws[threadIdx.x];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(FGC_FULL_MASK, y, o);
+                if (threadIdx.x >= o) y += t;
+            }
+            ws[threadIdx.x] = y;
+        }
+        __syncthreads();
+        const int warp_off = (threadIdx.x >> 5) ? ws[(threadIdx.x >> 5) - 1] : 0;
+        const int c = carry;
+        if (i < n) blocksums[i] = c + warp_off + incl - x;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = c + warp_off + incl;
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(256)
+k_scan_apply(int *__restrict__ counts, const KnnGrid *__restrict__ g,
+             const int *__restrict__ blocksums)
+{
+    const int n = g->total_bins + 1;
+    const int base = blockIdx.x * kScanTile;
+    if (base >= n) return;
+    constexpr int PER = kScanTile / 256;
+    int x[PER];
+    int s = 0;
+    const int first = base + threadIdx.x * PER;
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+        x[k] = first + k < n ? counts[first + k] : 0;
+        s += x[k];
+    }
+    int incl = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(FGC_FULL_MASK, incl, o);
+        if ((threadIdx.x & 31) >= o) incl += t;
+    }
+    __shared__ int ws[8];
+    if ((threadIdx.x & 31) == 31) ws[threadIdx.x >> 5] = incl;
+    __syncthreads();
+    int off = blocksums[blockIdx.x];
+    for (int k = 0; k < (int)(threadIdx.x >> 5); k++) off += ws[k];
+    int run = off + incl - s;
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+        if (first + k < n) counts[first + k] = run;
+        run += x[k];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+k_scatter(const float *__restrict__ coords, int n_vert, int n_coords, int nv,
+          const int64_t *__restrict__ direction, const KnnGrid *__restrict__ g,
+          const int *__restrict__ bounds, const int *__restrict__ pbin,
+          const int *__restrict__ prank, float4 *__restrict__ scoords, int *__restrict__ sorig,
+          int *__restrict__ sbin, uint8_t *__restrict__ sflag)
+{
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= n_vert || g->status != 0) return;
+    const int b = pbin[v];
+    const int pos = bounds[b] + prank[v];
+    const float *row = coords + (size_t)v * n_coords;
+    for (int q = 0; q < nv; q++) {
+        float4 o;
+        o.x = 4 * q + 0 < n_coords ? __ldg(row + 4 * q + 0) : 0.f;
+        o.y = 4 * q + 1 < n_coords ? __ldg(row + 4 * q + 1) : 0.f;
+        o.z = 4 * q + 2 < n_coords ? __ldg(row + 4 * q + 2) : 0.f;
+        o.w = 4 * q + 3 < n_coords ? __ldg(row + 4 * q + 3) : 0.f;
+        scoords[(size_t)pos * nv + q] = o;
+    }
+    sorig[pos] = v;
+    sbin[pos] = b;
+    if (direction) {
+        const int64_t d = direction[v];
+        sflag[pos] = (d >= 0 && d <= 2) ? (uint8_t)d : (uint8_t)3;
+    }
+}
+
+}  // namespace fgc
+
+extern "C" size_t fgc_knn_workspace_bytes(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K)
+{
+    if (n_vert < 0 || n_vert > 0x7fffffff || n_coords < 1 || n_rs < 1 || K < 1) return 0;
+    return fgc::knn_workspace_layout(n_vert, n_coords, n_rs, K).total;
+}
+
+extern "C" int fgc_read_status(const void *workspace_or_params, int32_t *status_host,
+                               fgc_stream_t stream)
+{
+    if (!workspace_or_params || !status_host) return FGC_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    FGC_RETURN_IF_CUDA(cudaMemcpyAsync(status_host, workspace_or_params, sizeof(int32_t),
+                                       cudaMemcpyDeviceToHost, s));
+    FGC_RETURN_IF_CUDA(cudaStreamSynchronize(s));
+    return FGC_OK;
+}
+
+extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n_coords,
+                                  const int64_t *row_splits, int64_t n_rs, int32_t K,
+                                  const int64_t *direction_or_null, float target_occupancy,
+                                  void *workspace, size_t workspace_bytes, fgc_stream_t stream)
+{
+    using namespace fgc;
+    KnnWorkspace L;
+    if (!row_splits) return FGC_ERR_BAD_ARGUMENT;
+    const int rc = check_knn_args(n_vert, n_coords, n_rs, K, workspace, workspace_bytes, &L);
+    if (rc != FGC_OK) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    char *ws = (char *)workspace;
+    KnnGrid *grid = (KnnGrid *)(ws + L.header);
+    FGC_RETURN_IF_CUDA(cudaMemsetAsync(grid, 0, kGridHeaderBytes, s));
+    if (n_vert == 0) return FGC_OK;
+    if (!coords || n_rs < 2) return FGC_ERR_BAD_ARGUMENT;
+
+    int *counts = (int *)(ws + L.counts);
+    int *blocksums = (int *)(ws + L.blocksums);
+    int *pbin = (int *)(ws + L.pbin);
+    int *prank = (int *)(ws + L.prank);
+    int *sorig = (int *)(ws + L.sorig);
+    int *sbin = (int *)(ws + L.sbin);
+    uint8_t *sflag = (uint8_t *)(ws + L.sflag);
+    float4 *scoords = (float4 *)(ws + L.scoords);
+
+    const int n = (int)n_vert;
+    const int n_events = (int)n_rs - 1;
+    const int n_bin_dims = n_coords < 3 ? n_coords : 3;
+    if (!(target_occupancy > 0.f)) target_occupancy = 2.0f;
+    const int64_t bins_cap64 = L.cap_bins / n_events;
+    const int bins_cap = (int)(bins_cap64 < 1 ? 1 : bins_cap64);
+    const double bt = (double)n_vert / (double)n_events / (double)target_occupancy;
+    int bins_target = bt >= (double)bins_cap ? bins_cap : (int)(bt + 0.5);
+    if (bins_target < 1) bins_target = 1;
+
+    const int pt_blocks = (n + 255) / 256;
+    const int red_blocks = pt_blocks < 148 * 4 ? pt_blocks : 148 * 4;
+    k_minmax<<<red_blocks, 256, 0, s>>>(coords, n, n_coords, n_bin_dims, grid);
+    FGC_CHECK_LAUNCH();
+    k_grid_setup<<<1, 32, 0, s>>>(grid, (int32_t *)(ws + L.shelltab), row_splits, (int)n_rs, n, n_bin_dims,
+                                  bins_target, bins_cap);
+    FGC_CHECK_LAUNCH();
+    // The cell count is only known on the device: the scan grids are sized for the
+    // largest table k_grid_setup may choose and surplus blocks return at once.
+    const int64_t max_entries = (int64_t)bins_cap * n_events + 1;
+    const int scan_blocks = (int)ceil_div64(max_entries, kScanTile);
+    k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid);
+    FGC_CHECK_LAUNCH();
+    k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
+                                          pbin, prank);
+    FGC_CHECK_LAUNCH();
+    k_scan_tile_sums<<<scan_blocks, 256, 0, s>>>(counts, grid, blocksums);
+    FGC_CHECK_LAUNCH();
+    k_scan_block_sums<<<1, 1024, 0, s>>>(blocksums, grid);
+    FGC_CHECK_LAUNCH();
+    k_scan_apply<<<scan_blocks, 256, 0, s>>>(counts, grid, blocksums);
+    FGC_CHECK_LAUNCH();
+    k_scatter<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, L.nv, direction_or_null, grid, counts,
+                                        pbin, prank, scoords, sorig, sbin, sflag);
+    FGC_CHECK_LAUNCH();
+    return FGC_OK;
+}
+
+extern "C" int fgc_knn_read_counters(const void *workspace, uint64_t *counters_host,
+                                     int32_t *grid_shape_host, float *cell_width_host,
+                                     fgc_stream_t stream)
+{
+    using namespace fgc;
+    if (!workspace) return FGC_ERR_BAD_ARGUMENT;
+    KnnGrid h;
+    cudaStream_t s = (cudaStream_t)stream;
+    FGC_RETURN_IF_CUDA(cudaMemcpyAsync(&h, workspace, sizeof(KnnGrid), cudaMemcpyDeviceToHost, s));
+    FGC_RETURN_IF_CUDA(cudaStreamSynchronize(s));
+    if (counters_host) for (int i = 0; i < 8; i++) counters_host[i] = h.counters[i];
+    if (grid_shape_host) { grid_shape_host[0] = h.n[0]; grid_shape_host[1] = h.n[1]; grid_shape_host[2] = h.n[2]; }
+    if (cell_width_host) *cell_width_host = h.w;
+    return FGC_OK;
+}

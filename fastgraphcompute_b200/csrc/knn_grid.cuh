@@ -29,8 +29,48 @@ struct KnnGrid {
     uint32_t min_key[3];   // ~ordered(min) per binned coordinate (atomicMax)
     uint32_t max_key[3];   // ordered(max)
     uint32_t nonfinite;    // set when any coordinate is NaN/Inf
-    unsigned long long n_evals;  // distance evaluations (debug counter, optional)
+    // optional debug counters (filled when a search is launched with count_evals):
+    // [0] distance evaluations, [1] 32-candidate steps, [2] list insertions,
+    // [3] 32-item metadata batches, [4] shells, [5] queries that scanned their whole row split
+    unsigned long long counters[8];
 };
+
+// Items of the Chebyshev shell of radius d around a cell, in units of "line segments": a
+// segment is a run of consecutive cells along the last grid dimension, i.e. one contiguous
+// range of sorted points.  Shell 0 is the cell itself.  For d >= 1 the 8d lines on the rim of
+// the (2d+1)x(2d+1) square of leading-dimension offsets contribute their whole 2d+1 cells,
+// every interior line contributes its two end cells.
+__host__ __device__ inline int shell_items(int d) { return d == 0 ? 1 : 8 * d + 2 * (2 * d - 1) * (2 * d - 1); }
+constexpr int kShellTableMaxD = 4;
+constexpr int kShellTableEntries = 1 + 10 + 34 + 74 + 130;   // sum of shell_items(0..4)
+__host__ __device__ inline int shell_table_offset(int d)
+{
+    return d == 0 ? 0 : (d == 1 ? 1 : (d == 2 ? 11 : (d == 3 ? 45 : 119)));
+}
+
+// Offsets (o0, o1) of the line and cell range [zlo, zhi] (relative to the query's cell) of
+// item u of shell d.
+__host__ __device__ inline void shell_item_decode(int d, int u, int &o0, int &o1, int &zlo, int &zhi)
+{
+    o0 = 0; o1 = 0; zlo = 0; zhi = 0;
+    if (d == 0) return;
+    const int side = 2 * d + 1, half = 2 * d - 1, n_ring = 8 * d;
+    if (u < n_ring) {
+        if (u < side) { o0 = -d; o1 = u - d; }
+        else if (u < 2 * side) { o0 = d; o1 = u - side - d; }
+        else {
+            const int t = u - 2 * side;
+            if (t < half) { o1 = -d; o0 = t - (d - 1); }
+            else { o1 = d; o0 = t - half - (d - 1); }
+        }
+        zlo = -d; zhi = d;
+    } else {
+        const int c = u - n_ring, t = c >> 1, tq = t / half;
+        o0 = tq - (d - 1);
+        o1 = t - tq * half - (d - 1);
+        zlo = zhi = (c & 1) ? d : -d;
+    }
+}
 
 constexpr size_t kGridHeaderBytes = 256;
 static_assert(sizeof(KnnGrid) <= kGridHeaderBytes, "grid header too large");
@@ -39,7 +79,7 @@ constexpr int kScanTile = 2048;  // elements per block in the 3-kernel scan
 
 // Byte offsets of the workspace sections (all 256-byte aligned).
 struct KnnWorkspace {
-    size_t header, counts, blocksums, pbin, prank, sorig, sbin, sflag, scoords, total;
+    size_t header, shelltab, counts, blocksums, pbin, prank, sorig, sbin, sflag, scoords, total;
     int64_t cap_bins;   // capacity of the cell table (entries), host decision
     int nv;             // float4 per point in the sorted coordinate array
 };
@@ -56,6 +96,7 @@ inline KnnWorkspace knn_workspace_layout(int64_t n_vert, int n_coords, int64_t n
     w.nv = (n_coords + 3) / 4;
     size_t off = 0;
     w.header = off; off += kGridHeaderBytes;
+    w.shelltab = off; off = align_up(off + sizeof(int32_t) * kShellTableEntries, 256);
     w.counts = off; off = align_up(off + sizeof(int32_t) * (size_t)(cap + 1), 256);
     w.blocksums = off; off = align_up(off + sizeof(int32_t) * (size_t)((cap + 1) / kScanTile + 2), 256);
     w.pbin = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
@@ -66,6 +107,20 @@ inline KnnWorkspace knn_workspace_layout(int64_t n_vert, int n_coords, int64_t n
     w.scoords = off; off = align_up(off + sizeof(float4) * (size_t)n_vert * w.nv, 256);
     w.total = off;
     return w;
+}
+
+// Argument checks shared by the kNN entry points.
+inline int check_knn_args(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
+                          const void *workspace, size_t workspace_bytes, KnnWorkspace *L)
+{
+    if (n_vert < 0 || n_rs < 1) return FGC_ERR_BAD_ARGUMENT;
+    if (n_vert > 0x7fffffff || n_rs > 0x7fffffff) return FGC_ERR_TOO_LARGE;
+    if (n_coords < 2) return n_coords < 1 ? FGC_ERR_BAD_ARGUMENT : FGC_ERR_UNSUPPORTED_DIM;
+    if (n_coords > 8) return FGC_ERR_UNSUPPORTED_DIM;
+    if (K < 1 || K > FGC_MAX_K) return FGC_ERR_UNSUPPORTED_K;
+    *L = knn_workspace_layout(n_vert, n_coords, n_rs, K);
+    if (!workspace || workspace_bytes < L->total || ((uintptr_t)workspace & 255)) return FGC_ERR_WORKSPACE;
+    return FGC_OK;
 }
 
 }  // namespace fgc

@@ -1,0 +1,426 @@
+// binned_select_knn forward for sm_100a, part 2: the neighbour search on a built grid
+// (knn_grid.cu builds it).
+//
+// One warp per query point.  The warp walks the cells around the query's cell in
+// expanding Chebyshev shells.  A shell is described as "items" -- runs of cells along
+// the last grid dimension, each a contiguous range of cell-sorted points -- and 32 items
+// are looked up at once (one per lane: bounds check, distance-to-box pruning against the
+// current K-th distance, two loads of the cell boundaries).  The non-empty ranges of a
+// batch are then treated as one flattened candidate stream: every step each lane takes
+// the next candidate (a 16-byte load per float4 of coordinates), evaluates the squared
+// distance and the warp votes on which candidates beat the current K-th distance.  The
+// K-1 best live in registers, spread over the lanes.  The search of a query ends as soon
+// as the cube of cells it has covered contains the ball of its K-th distance.
+//
+// What is computed is what the reference's CPU path computes
+// (extensions/binned_knn_autograd_kernel.cpp:85-209 with
+// extensions/binned_select_knn_cpu.cpp:56-208): per row split, the K-1 nearest other
+// points, strict "<" replacement of the current worst (so among equal distances the one
+// visited first stays), squared distances accumulated over the dimensions in order with
+// one rounding per operation.  Visiting order, grid and stopping rule are this library's
+// own; they never change which points are nearest, only which of several equidistant
+// points is kept.
+#include "knn_grid.cuh"
+
+namespace fgc {
+
+struct KnnArgs {
+    const float4 *scoords;
+    const int *sorig;
+    const int *sbin;
+    const uint8_t *sflag;   // nullptr: no direction restriction
+    const int *bounds;      // cell boundaries, total_bins + 1 entries
+    const int32_t *shelltab;
+    KnnGrid *grid;
+    int64_t *out_idx;
+    float *out_dist;
+    int n_vert;
+    int K;
+    int n_coords;
+    int tf_compat;
+    int count_evals;
+};
+
+constexpr int kKnnWarps = 8;
+constexpr uint32_t kInfBits = 0x7f800000u;
+
+// Squared distance over NV float4 chunks.  Order and rounding: acc = acc + (a-b)*(a-b)
+// per dimension, dimension 0 first, no fused multiply-add; the first term needs no add.
+template <int NV>
+__device__ __forceinline__ float dist_sq(const float4 (&q)[NV], const float4 (&c)[NV], int n_coords)
+{
+    float d = __fsub_rn(q[0].x, c[0].x);
+    float acc = __fmul_rn(d, d);
+    d = __fsub_rn(q[0].y, c[0].y); acc = __fadd_rn(acc, __fmul_rn(d, d));   // n_coords >= 2
+    if (2 < n_coords) { d = __fsub_rn(q[0].z, c[0].z); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
+    if (3 < n_coords) { d = __fsub_rn(q[0].w, c[0].w); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
+#pragma unroll
+    for (int v = 1; v < NV; v++) {
+        if (4 * v + 0 < n_coords) { d = __fsub_rn(q[v].x, c[v].x); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
+        if (4 * v + 1 < n_coords) { d = __fsub_rn(q[v].y, c[v].y); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
+        if (4 * v + 2 < n_coords) { d = __fsub_rn(q[v].z, c[v].z); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
+        if (4 * v + 3 < n_coords) { d = __fsub_rn(q[v].w, c[v].w); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
+    }
+    return acc;
+}
+
+// The per-warp neighbour list: slot s = lane*R + r (r < R) is valid when s < K-1.
+// Empty valid slots hold +inf, invalid slots hold +0 and are never chosen.  tau is the
+// largest stored distance, compared through the bit pattern (monotone for non-negative
+// floats), so while a slot is empty tau is +inf and every candidate goes to the first
+// empty slot; afterwards a candidate replaces the first slot that holds tau iff its
+// distance is strictly smaller.  Slots fill in slot order, so empty slots are a suffix.
+template <int R>
+struct NeighbourList {
+    float d[R];
+    int id[R];
+    uint32_t lmax;   // max bit pattern over this lane's slots
+    uint32_t tau;    // max over the warp
+    int filled;      // number of occupied slots (warp-uniform)
+
+    __device__ __forceinline__ void init(int lane, int kn)
+    {
+        lmax = 0;
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            d[r] = (lane * R + r < kn) ? __uint_as_float(kInfBits) : 0.f;
+            id[r] = -1;
+            lmax = max(lmax, __float_as_uint(d[r]));
+        }
+        tau = __reduce_max_sync(FGC_FULL_MASK, lmax);
+        filled = 0;
+    }
+
+    __device__ __forceinline__ void refresh(int lane)
+    {
+        uint32_t m = 0;
+#pragma unroll
+        for (int r = 0; r < R; r++) m = max(m, __float_as_uint(d[r]));
+        lmax = m;
+        tau = __reduce_max_sync(FGC_FULL_MASK, lmax);
+    }
+
+    // Warp-uniform: insert candidate (dc, jc) if dc < tau.  Returns 1 if inserted.
+    __device__ __forceinline__ int offer(int lane, float dc, int jc)
+    {
+        if (__float_as_uint(dc) >= tau) return 0;
+        const unsigned holders = __ballot_sync(FGC_FULL_MASK, lmax == tau);
+        if (lane == __ffs(holders) - 1) {
+            bool done = false;
+            uint32_t m = 0;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                if (!done && __float_as_uint(d[r]) == tau) { d[r] = dc; id[r] = jc; done = true; }
+                m = max(m, __float_as_uint(d[r]));
+            }
+            lmax = m;
+        }
+        filled += tau == kInfBits ? 1 : 0;
+        tau = __reduce_max_sync(FGC_FULL_MASK, lmax);
+        return 1;
+    }
+};
+
+template <int NV, int R, bool COUNT>
+__global__ void __launch_bounds__(kKnnWarps * 32, (R <= 2 ? 5 : 3))
+k_knn(const KnnArgs a)
+{
+    __shared__ int s_delta[kKnnWarps][32];
+    __shared__ float s_bd[kKnnWarps][32];
+    __shared__ int s_bj[kKnnWarps][32];
+    const int lane = threadIdx.x & 31;
+    const int wib = threadIdx.x >> 5;
+    const int qi = blockIdx.x * kKnnWarps + wib;   // position in cell order
+    KnnGrid *__restrict__ g = a.grid;
+    if (qi >= a.n_vert || g->status != 0) return;
+
+    const int K = a.K, kn = K - 1;
+    const int nc = a.n_coords;
+    const uint8_t *__restrict__ sflag = a.sflag;
+    const int orig_q = __ldg(a.sorig + qi);
+    int64_t *__restrict__ out_i = a.out_idx + (size_t)orig_q * K;
+    float *__restrict__ out_d = a.out_dist + (size_t)orig_q * K;
+
+    // queries that may not have neighbours keep the default row
+    const bool q_inactive = sflag && (sflag[qi] == 0 || sflag[qi] == 2);
+
+    float4 q[NV];
+#pragma unroll
+    for (int v = 0; v < NV; v++) q[v] = __ldg(a.scoords + (size_t)qi * NV + v);
+
+    NeighbourList<R> list;
+    list.init(lane, kn);
+    unsigned cnt_evals = 0, cnt_steps = 0, cnt_ins = 0, cnt_batches = 0, cnt_shells = 0, cnt_brute = 0;
+
+    // one step: lane evaluates the candidate at sorted position j (if act)
+    auto process = [&](int j, bool act) {
+        float dc = __uint_as_float(kInfBits);
+        if (act) {
+            float4 c[NV];
+#pragma unroll
+            for (int v = 0; v < NV; v++) c[v] = __ldg(a.scoords + (size_t)j * NV + v);
+            bool ok = j != qi;
+            if (sflag) { const uint8_t f = sflag[j]; ok = ok && f != 1 && f != 2; }
+            if (ok) dc = dist_sq<NV>(q, c, nc);
+        }
+        if (COUNT) { cnt_evals += act ? 1 : 0; cnt_steps += 1; }
+        unsigned m = __ballot_sync(FGC_FULL_MASK, __float_as_uint(dc) < list.tau);
+        if (m == 0) return;
+        const int npass = __popc(m);
+        if (R >= 2 && list.filled + npass <= kn) {
+            // all passing candidates fit into empty slots (tau is +inf here): place them in
+            // one go through shared memory instead of one warp-wide insertion each (pays
+            // off once a lane holds more than one slot)
+            if (m >> lane & 1) {
+                const int rk = __popc(m & lanemask_lt());
+                s_bd[wib][rk] = dc;
+                s_bj[wib][rk] = j;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const int src = lane * R + r - list.filled;
+                if (src >= 0 && src < npass) { list.d[r] = s_bd[wib][src]; list.id[r] = s_bj[wib][src]; }
+            }
+            __syncwarp();
+            list.filled += npass;
+            list.refresh(lane);
+            if (COUNT) cnt_ins += npass;
+            return;
+        }
+        while (m) {
+            const int src = __ffs(m) - 1;
+            m &= m - 1;
+            const float dcs = __shfl_sync(FGC_FULL_MASK, dc, src);
+            const int js = __shfl_sync(FGC_FULL_MASK, j, src);
+            const int ins = list.offer(lane, dcs, js);
+            if (COUNT) cnt_ins += ins;
+        }
+    };
+
+    if (!q_inactive && kn > 0) {
+        const int B = g->B, n0 = g->n[0], n1 = g->n[1], n2 = g->n[2];
+        const int flat = __ldg(a.sbin + qi);
+        const int e = flat / B;
+        int rem = flat - e * B;
+        const int b0 = rem / (n1 * n2);
+        rem -= b0 * n1 * n2;
+        const int b1 = rem / n2;
+        const int b2 = rem - b1 * n2;
+        const int ev_begin = __ldg(a.bounds + e * B);
+        const int ev_end = __ldg(a.bounds + (e + 1) * B);
+        const int n_e = ev_end - ev_begin;
+
+        bool brute = n_e <= 512 || n_e <= 8 * K;
+        if (!brute) {
+            const float w = g->w, slack = g->slack;
+            const float w_lo = w * (1.0f - 1e-6f), w_hi = w * (1.0f + 1e-6f);
+            // query position relative to the grid origin, per grid dimension
+            float qr[3];
+            {
+                const float qc[3] = {q[0].x, q[0].y, q[0].z};
+#pragma unroll
+                for (int gd = 0; gd < 3; gd++) {
+                    const int c = g->cdim[gd];
+                    const float x = c == 0 ? qc[0] : (c == 1 ? qc[1] : qc[2]);
+                    qr[gd] = c < 0 ? 0.f : __fsub_rn(x, g->origin[gd]);
+                }
+            }
+            // Points of cell b have a shifted coordinate >= b*w and < (b+1)*w up to fp32
+            // rounding of the cell index computation; the bounds below widen the cell by a
+            // relative 1e-6 and an absolute slack so that they hold for every such point.
+            // gap_to: lower bound of |x - query| over the points of cells [lo, hi].
+            auto gap_to = [&](int lo, int hi, int bq, float qrel) {
+                float gp = 0.f;
+                if (lo > bq) gp = (float)lo * w_lo - qrel - slack;
+                else if (hi < bq) gp = qrel - (float)(hi + 1) * w_hi - slack;
+                return fmaxf(gp, 0.f);
+            };
+            long long items_done = 0;
+            for (int d = 0;; ++d) {
+                const int n_items = shell_items(d);
+                const int32_t *tab = d <= kShellTableMaxD ? a.shelltab + shell_table_offset(d) : nullptr;
+                for (int base = 0; base < n_items; base += 32) {
+                    const int u = base + lane;
+                    bool valid = u < n_items;
+                    int o0 = 0, o1 = 0, zlo = 0, zhi = 0;
+                    if (valid) {
+                        if (tab) {
+                            const int32_t t = __ldg(tab + u);
+                            o0 = (int)(int8_t)(t & 0xff);
+                            o1 = (int)(int8_t)((t >> 8) & 0xff);
+                            zlo = (int)(int8_t)((t >> 16) & 0xff);
+                            zhi = (int)(int8_t)((t >> 24) & 0xff);
+                        } else {
+                            shell_item_decode(d, u, o0, o1, zlo, zhi);
+                        }
+                    }
+                    const int g0 = b0 + o0, g1 = b1 + o1;
+                    valid = valid && g0 >= 0 && g0 < n0 && g1 >= 0 && g1 < n1;
+                    zlo = max(b2 + zlo, 0);
+                    zhi = min(b2 + zhi, n2 - 1);
+                    valid = valid && zlo <= zhi;
+                    if (valid && list.tau < kInfBits) {
+                        const float ga = gap_to(g0, g0, b0, qr[0]);
+                        const float gb = gap_to(g1, g1, b1, qr[1]);
+                        const float gc = gap_to(zlo, zhi, b2, qr[2]);
+                        const float md = ga * ga + gb * gb + gc * gc;
+                        if (md > __uint_as_float(list.tau) * 1.00001f) valid = false;
+                    }
+                    int start = 0, len = 0;
+                    if (valid) {
+                        const int rowbase = e * B + (g0 * n1 + g1) * n2;
+                        start = __ldg(a.bounds + rowbase + zlo);
+                        len = __ldg(a.bounds + rowbase + zhi + 1) - start;
+                    }
+                    const unsigned nzm = __ballot_sync(FGC_FULL_MASK, len > 0);
+                    if (nzm == 0) continue;
+                    if (COUNT) cnt_batches += 1;
+                    int incl = len;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int t = __shfl_up_sync(FGC_FULL_MASK, incl, o);
+                        if (lane >= o) incl += t;
+                    }
+                    const int T = __shfl_sync(FGC_FULL_MASK, incl, 31);
+                    const int pprev = incl - len;
+                    if (len > 0) s_delta[wib][__popc(nzm & lanemask_lt())] = start - pprev;
+                    __syncwarp();
+                    int rbase = 0;
+                    for (int t = 0; t < T; t += 32) {
+                        // which range does flattened position t + lane belong to: mark the
+                        // positions inside this step where a range starts
+                        const int rel = pprev - t;
+                        const unsigned contrib = (len > 0 && rel >= 0 && rel < 32) ? (1u << rel) : 0u;
+                        const unsigned M = __reduce_or_sync(FGC_FULL_MASK, contrib);
+                        const int r = rbase + __popc(M & lanemask_le()) - 1;
+                        rbase += __popc(M);
+                        const int c = t + lane;
+                        const bool act = c < T;
+                        const int j = act ? c + s_delta[wib][r] : -1;
+                        process(j, act);
+                    }
+                    __syncwarp();
+                }
+                items_done += n_items;
+                if (COUNT) cnt_shells += 1;
+                // every point outside the cube of radius d is at least fd away
+                float fd = __uint_as_float(kInfBits);
+                bool any = false;
+                {
+                    const int bq[3] = {b0, b1, b2};
+                    const int nn[3] = {n0, n1, n2};
+#pragma unroll
+                    for (int gd = 0; gd < 3; gd++) {
+                        const int hi = bq[gd] + d + 1, lo = bq[gd] - d - 1;
+                        if (hi <= nn[gd] - 1) { fd = fminf(fd, fmaxf((float)hi * w_lo - qr[gd] - slack, 0.f)); any = true; }
+                        if (lo >= 0) { fd = fminf(fd, fmaxf(qr[gd] - (float)(lo + 1) * w_hi - slack, 0.f)); any = true; }
+                    }
+                }
+                if (!any) break;
+                if (list.tau < kInfBits && fd * fd > __uint_as_float(list.tau) * 1.00001f) break;
+                // walking mostly empty cells: scanning the whole row split is cheaper
+                if (items_done * 8 > (long long)n_e) { brute = true; break; }
+            }
+            if (brute) list.init(lane, kn);
+        }
+        if (brute) {
+            if (COUNT) cnt_brute = 1;
+            for (int t = 0; t < n_e; t += 32) {
+                const int c = t + lane;
+                process(ev_begin + c, c < n_e);
+            }
+        }
+    }
+
+    // epilogue: original ids, original row position
+    if (lane == 0) { out_i[0] = orig_q; out_d[0] = 0.f; }
+    const int64_t pad = a.tf_compat ? (int64_t)orig_q : (int64_t)-1;
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const int s = lane * R + r;
+        if (s < kn) {
+            const bool filled = __float_as_uint(list.d[r]) < kInfBits && list.id[r] >= 0;
+            out_i[1 + s] = filled ? (int64_t)__ldg(a.sorig + list.id[r]) : pad;
+            out_d[1 + s] = filled ? list.d[r] : 0.f;
+        }
+    }
+    if (COUNT) {
+        cnt_evals = __reduce_add_sync(FGC_FULL_MASK, cnt_evals);
+        if (lane == 0) {
+            atomicAdd(&g->counters[0], (unsigned long long)cnt_evals);
+            atomicAdd(&g->counters[1], (unsigned long long)cnt_steps);
+            atomicAdd(&g->counters[2], (unsigned long long)cnt_ins);
+            atomicAdd(&g->counters[3], (unsigned long long)cnt_batches);
+            atomicAdd(&g->counters[4], (unsigned long long)cnt_shells);
+            atomicAdd(&g->counters[5], (unsigned long long)cnt_brute);
+        }
+    }
+}
+
+template <int NV>
+static int launch_knn_nv(const KnnArgs &a, cudaStream_t s)
+{
+    const int kn = a.K - 1;
+    const unsigned blocks = (unsigned)((a.n_vert + kKnnWarps - 1) / kKnnWarps);
+    const int R = (kn + 31) / 32;
+    const int T = kKnnWarps * 32;
+    if (a.count_evals) {
+        if (R <= 1) k_knn<NV, 1, true><<<blocks, T, 0, s>>>(a);
+        else if (R <= 2) k_knn<NV, 2, true><<<blocks, T, 0, s>>>(a);
+        else if (R <= 4) k_knn<NV, 4, true><<<blocks, T, 0, s>>>(a);
+        else k_knn<NV, 8, true><<<blocks, T, 0, s>>>(a);
+    } else {
+        if (R <= 1) k_knn<NV, 1, false><<<blocks, T, 0, s>>>(a);
+        else if (R <= 2) k_knn<NV, 2, false><<<blocks, T, 0, s>>>(a);
+        else if (R <= 4) k_knn<NV, 4, false><<<blocks, T, 0, s>>>(a);
+        else k_knn<NV, 8, false><<<blocks, T, 0, s>>>(a);
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace fgc
+
+extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
+                              int32_t has_direction, int32_t tf_compat, int32_t count_evals,
+                              int64_t *out_idx, float *out_distsq, void *workspace,
+                              size_t workspace_bytes, fgc_stream_t stream)
+{
+    using namespace fgc;
+    KnnWorkspace L;
+    const int rc = check_knn_args(n_vert, n_coords, n_rs, K, workspace, workspace_bytes, &L);
+    if (rc != FGC_OK) return rc;
+    if (n_vert == 0) return FGC_OK;
+    if (!out_idx || !out_distsq) return FGC_ERR_BAD_ARGUMENT;
+    char *ws = (char *)workspace;
+    KnnArgs a;
+    a.scoords = (const float4 *)(ws + L.scoords);
+    a.sorig = (const int *)(ws + L.sorig);
+    a.sbin = (const int *)(ws + L.sbin);
+    a.sflag = has_direction ? (const uint8_t *)(ws + L.sflag) : nullptr;
+    a.bounds = (const int *)(ws + L.counts);
+    a.shelltab = (const int32_t *)(ws + L.shelltab);
+    a.grid = (KnnGrid *)(ws + L.header);
+    a.out_idx = out_idx;
+    a.out_dist = out_distsq;
+    a.n_vert = (int)n_vert;
+    a.K = K;
+    a.n_coords = n_coords;
+    a.tf_compat = tf_compat;
+    a.count_evals = count_evals;
+    return L.nv == 1 ? launch_knn_nv<1>(a, (cudaStream_t)stream)
+                     : launch_knn_nv<2>(a, (cudaStream_t)stream);
+}
+
+extern "C" int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,
+                                  const int64_t *row_splits, int64_t n_rs, int32_t K,
+                                  const int64_t *direction_or_null, int32_t tf_compat,
+                                  float target_occupancy, int64_t *out_idx, float *out_distsq,
+                                  void *workspace, size_t workspace_bytes, fgc_stream_t stream)
+{
+    int rc = fgc_knn_build_grid(coords, n_vert, n_coords, row_splits, n_rs, K, direction_or_null,
+                                target_occupancy, workspace, workspace_bytes, stream);
+    if (rc != FGC_OK) return rc;
+    return fgc_knn_search(n_vert, n_coords, n_rs, K, direction_or_null != nullptr, tf_compat, 0,
+                          out_idx, out_distsq, workspace, workspace_bytes, stream);
+}

@@ -74,15 +74,16 @@ def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=Fal
 
 
 def read_counters(ws):
-    """(distance evaluations, grid shape [3], cell width) of a forward's workspace."""
-    n_evals = ctypes.c_uint64(0)
+    """(counters [8], grid shape [3], cell width) of a forward's workspace; counters[0] is the
+    number of distance evaluations of a search launched with count_evals."""
+    counters = (ctypes.c_uint64 * 8)()
     shape = (ctypes.c_int32 * 3)()
     width = ctypes.c_float(0)
     with torch.cuda.device(ws.device):
         _cabi.check(_cabi.lib.fgc_knn_read_counters(
-            _cabi.ptr(ws), ctypes.byref(n_evals), shape, ctypes.byref(width),
+            _cabi.ptr(ws), counters, shape, ctypes.byref(width),
             _cabi.current_stream(ws.device)), "fgc_knn_read_counters")
-    return n_evals.value, [shape[0], shape[1], shape[2]], width.value
+    return list(counters), [shape[0], shape[1], shape[2]], width.value
 
 
 class _BinnedKNN(torch.autograd.Function):

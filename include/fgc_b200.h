@@ -164,11 +164,13 @@ int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
                    size_t workspace_bytes, fgc_stream_t stream);
 
 /*
- * Diagnostics of a built workspace, copied to the host (synchronises the stream): the
- * distance-evaluation counter, the grid shape [3] and the cell width.  Any output pointer
- * may be NULL.  No counterpart in the reference.
+ * Diagnostics of a workspace, copied to the host (synchronises the stream): eight 64-bit
+ * counters that a search launched with count_evals != 0 accumulates ([0] distance
+ * evaluations, [1] 32-candidate steps, [2] list insertions, [3] metadata batches, [4] shells,
+ * [5] queries that scanned their whole row split), the grid shape [3] and the cell width.
+ * Any output pointer may be NULL.  No counterpart in the reference.
  */
-int fgc_knn_read_counters(const void *workspace, uint64_t *n_evals_host,
+int fgc_knn_read_counters(const void *workspace, uint64_t *counters_host,
                           int32_t *grid_shape_host, float *cell_width_host,
                           fgc_stream_t stream);
 
