@@ -48,6 +48,8 @@ ERR_UNSUPPORTED_DIM = -2
 ERR_UNSUPPORTED_K = -3
 ERR_WORKSPACE = -4
 ERR_TOO_LARGE = -5
+ERR_STATIC_TOO_LARGE = -6
+STATIC_WORKSPACE_BYTES = 4 << 20
 
 
 class BinParams(ctypes.Structure):
@@ -82,6 +84,9 @@ SIGNATURES = {
     "fgc_knn_read_counters": (ctypes.c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint64),
                                              ctypes.POINTER(c_i32), ctypes.POINTER(c_float),
                                              c_void_p]),
+    "fgc_binned_knn_fwd_static": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_void_p, c_i64, c_i32,
+                                                 c_void_p, c_i32, c_float, c_void_p, c_void_p,
+                                                 c_void_p, c_void_p]),
     "fgc_read_status": (ctypes.c_int, [c_void_p, ctypes.POINTER(c_i32), c_void_p]),
     "fgc_binned_knn_bwd": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i32, c_i32,
                                           c_void_p, c_void_p]),

@@ -38,6 +38,7 @@ extern "C" {
 #define FGC_ERR_UNSUPPORTED_K (-3)  /* K < 1 or K > FGC_MAX_K */
 #define FGC_ERR_WORKSPACE (-4)      /* workspace too small / misaligned */
 #define FGC_ERR_TOO_LARGE (-5)      /* n_vert or a bin table exceeds 2^31-1 entries */
+#define FGC_ERR_STATIC_TOO_LARGE (-6) /* fgc_binned_knn_fwd_static: problem needs more than FGC_STATIC_WORKSPACE_BYTES */
 
 /* bits of the device status word */
 #define FGC_STATUS_NONFINITE 1      /* a coordinate is NaN or +-Inf */
@@ -173,6 +174,35 @@ int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
 int fgc_knn_read_counters(const void *workspace, uint64_t *counters_host,
                           int32_t *grid_shape_host, float *cell_width_host,
                           fgc_stream_t stream);
+
+/*
+ * kNN forward without a caller-provided workspace and without any allocation.
+ * (No counterpart in the reference, whose ops allocate through PyTorch.)
+ *
+ * For hosts that cannot allocate device memory at call time -- services and online event
+ * filters that fix their memory budget at start-up, or plugins that are only handed input
+ * and output pointers -- the scratch lives in a fixed array inside the library image
+ * (FGC_STATIC_WORKSPACE_BYTES per GPU, held by every GPU that loads the library until the
+ * process exits).  Same inputs, outputs and results as fgc_binned_knn_fwd, plus
+ *   out_status : [1] int32 in device memory, receives the FGC_STATUS_* word of the call.
+ * Limits and rules:
+ *   - returns FGC_ERR_STATIC_TOO_LARGE when fgc_knn_workspace_bytes(n_vert, n_coords, n_rs, K)
+ *     exceeds FGC_STATIC_WORKSPACE_BYTES (that is at about 60 000 points with up to 4
+ *     coordinates and about 48 000 with 5 to 8); nothing is launched in that case;
+ *   - calls no cudaMalloc/cudaFree or other allocating routine;
+ *   - the first call on each GPU looks up the device address of the array
+ *     (cudaGetSymbolAddress, with that GPU current); make that first call outside any
+ *     stream capture;
+ *   - all calls on one GPU share the one array: calls that can overlap on the GPU (different
+ *     streams or host threads) race and must be serialised by the caller.  The array keeps
+ *     the previous call's contents; each call clears the parts it relies on being zero.
+ */
+#define FGC_STATIC_WORKSPACE_BYTES (4u << 20)
+int fgc_binned_knn_fwd_static(const float *coords, int64_t n_vert, int32_t n_coords,
+                              const int64_t *row_splits, int64_t n_rs, int32_t K,
+                              const int64_t *direction_or_null, int32_t tf_compat,
+                              float target_occupancy, int64_t *out_idx, float *out_distsq,
+                              int32_t *out_status, fgc_stream_t stream);
 
 /*
  * Copies the status word at the start of a workspace / fgc_bin_params to the
