@@ -68,6 +68,22 @@ k_minmax(const float *__restrict__ coords, int n_vert, int n_coords, int n_bin_d
     if (threadIdx.x == 0 && s_bad) atomicOr(&g->nonfinite, 1u);
 }
 
+// Cells per dimension for a wanted cell width; widens the cells until the table fits.
+__device__ inline void fit_shape(const float (&ext)[3], double wd, int bins_cap, int (&n)[3], float &w)
+{
+    for (int iter = 0; iter < 400; iter++) {
+        w = (float)wd;
+        const float inv = __fdiv_rn(1.0f, w);
+        double prod = 1.0;
+        for (int gd = 0; gd < 3; gd++) {
+            n[gd] = ext[gd] > 0.f ? (int)floorf(__fmul_rn(ext[gd], inv)) + 1 : 1;
+            prod *= (double)n[gd];
+        }
+        if (prod <= (double)bins_cap) break;
+        wd *= 1.05;
+    }
+}
+
 // One thread.  Chooses the cell width so that a row split of average size gets
 // about bins_target cells, bounded by bins_cap cells per row split.
 __global__ void __launch_bounds__(32)
@@ -123,17 +139,7 @@ k_grid_setup(KnnGrid *g, int32_t *__restrict__ shelltab, const int64_t *__restri
         double wd = pow(vol / (double)bins_target, 1.0 / (double)nz);
         // a degenerate extent ratio can make the width underflow: keep it representable
         if (!(wd > (double)ext_max * 1e-6)) wd = (double)ext_max * 1e-6;
-        for (int iter = 0; iter < 400; iter++) {
-            w = (float)wd;
-            const float inv = __fdiv_rn(1.0f, w);
-            double prod = 1.0;
-            for (int gd = 0; gd < 3; gd++) {
-                n[gd] = ext[gd] > 0.f ? (int)floorf(__fmul_rn(ext[gd], inv)) + 1 : 1;
-                prod *= (double)n[gd];
-            }
-            if (prod <= (double)bins_cap) break;
-            wd *= 1.05;
-        }
+        fit_shape(ext, wd, bins_cap, n, w);
     }
     long long B = (long long)n[0] * n[1] * n[2];
     if (B > bins_cap) {  // cannot happen after the loop above unless the extents are absurd
@@ -147,11 +153,68 @@ k_grid_setup(KnnGrid *g, int32_t *__restrict__ shelltab, const int64_t *__restri
     g->w = w;
     g->inv_w = __fdiv_rn(1.0f, w);
     g->slack = 4e-6f * fmaxf(ext_max, w);
+    g->ext[0] = ext[0]; g->ext[1] = ext[1]; g->ext[2] = ext[2];
+    g->bins_cap = bins_cap;
     g->status = status;
 }
 
-__global__ void __launch_bounds__(256) k_zero_counts(int *__restrict__ counts, const KnnGrid *g)
+// Density pass.  The first grid is sized from the bounding box, i.e. from the MEAN density.
+// Clustered data puts most points into cells far above that mean, and the cost of a query
+// grows with the occupancy of the cells around it.  sum_c c^2 / N is the occupancy a typical
+// point sees in its own cell; when it is well above the wanted value the grid is rebuilt
+// with cells shrunk by the cube root of the ratio (occupancy scales with the cell volume
+// where the density is locally smooth).
+__global__ void __launch_bounds__(256) k_cell_stat(const int *__restrict__ counts, KnnGrid *g)
 {
+    if (g->status != 0) return;
+    const int n = g->total_bins;
+    unsigned long long s = 0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const unsigned long long c = (unsigned long long)counts[i];
+        s += c * c;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FGC_FULL_MASK, s, o);
+    if ((threadIdx.x & 31) == 0 && s) atomicAdd(&g->sum_sq, s);
+}
+
+__global__ void k_grid_refine(KnnGrid *g, int n_vert, float seen_target)
+{
+    if (threadIdx.x != 0 || blockIdx.x != 0 || g->status != 0) return;
+    const double seen = (double)g->sum_sq / (double)(n_vert > 0 ? n_vert : 1);
+    if (!(seen > 1.5 * (double)seen_target)) return;
+    int nz = 0;
+    float ext[3], ext_max = 0.f;
+    for (int gd = 0; gd < 3; gd++) {
+        ext[gd] = g->ext[gd];
+        if (ext[gd] > 0.f) nz++;
+        ext_max = fmaxf(ext_max, ext[gd]);
+    }
+    if (nz == 0) return;
+    double shrink = pow((double)seen_target / seen, 1.0 / (double)nz);
+    // Never more than 2.2x: data that mixes very dense clusters with a thin background
+    // would otherwise pay with long walks through empty cells for the background queries.
+    if (shrink < 1.0 / 2.2) shrink = 1.0 / 2.2;
+    double wd = (double)g->w * shrink;
+    if (!(wd > (double)ext_max * 1e-6)) wd = (double)ext_max * 1e-6;
+    int n[3] = {1, 1, 1};
+    float w = g->w;
+    fit_shape(ext, wd, g->bins_cap, n, w);
+    const long long B = (long long)n[0] * n[1] * n[2];
+    if (B > g->bins_cap || !(w < g->w)) return;
+    g->n[0] = n[0]; g->n[1] = n[1]; g->n[2] = n[2];
+    g->B = (int)B;
+    g->total_bins = (int)(B * g->n_events);
+    g->w = w;
+    g->inv_w = __fdiv_rn(1.0f, w);
+    g->slack = 4e-6f * fmaxf(ext_max, w);
+    g->refined = 1;
+}
+
+__global__ void __launch_bounds__(256)
+k_zero_counts(int *__restrict__ counts, const KnnGrid *g, int only_if_refined)
+{
+    if (only_if_refined && !g->refined) return;
     const int n = g->total_bins + 1;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         counts[i] = 0;
@@ -169,8 +232,10 @@ __device__ __forceinline__ int cell_of(float x, float origin, float inv_w, int n
 __global__ void __launch_bounds__(256)
 k_histogram(const float *__restrict__ coords, int n_vert, int n_coords,
             const int64_t *__restrict__ row_splits, int n_rs, const KnnGrid *__restrict__ g,
-            int *__restrict__ counts, int *__restrict__ pbin, int *__restrict__ prank)
+            int *__restrict__ counts, int *__restrict__ pbin, int *__restrict__ prank,
+            int only_if_refined)
 {
+    if (only_if_refined && !g->refined) return;
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     const bool live = v < n_vert && g->status == 0;
     int flat = 0;
@@ -374,7 +439,14 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
     const int n = (int)n_vert;
     const int n_events = (int)n_rs - 1;
     const int n_bin_dims = n_coords < 3 ? n_coords : 3;
-    if (!(target_occupancy > 0.f)) target_occupancy = 2.0f;
+    // target_occupancy > 0: one fixed grid with that mean occupancy.  Otherwise: mean
+    // occupancy 2, then the density pass may shrink the cells so that a typical point sees
+    // about seen_target points in its own cell.
+    const bool adaptive = !(target_occupancy > 0.f);
+    if (adaptive) target_occupancy = 2.0f;
+    float seen_target = (float)K / 6.0f;
+    if (seen_target < 4.f) seen_target = 4.f;
+    if (n_coords > 3) seen_target *= 2.f;   // coordinates beyond the binned three thin the cells out
     const int64_t bins_cap64 = L.cap_bins / n_events;
     const int bins_cap = (int)(bins_cap64 < 1 ? 1 : bins_cap64);
     const double bt = (double)n_vert / (double)n_events / (double)target_occupancy;
@@ -392,11 +464,22 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
     // largest table k_grid_setup may choose and surplus blocks return at once.
     const int64_t max_entries = (int64_t)bins_cap * n_events + 1;
     const int scan_blocks = (int)ceil_div64(max_entries, kScanTile);
-    k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid);
+    k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid, 0);
     FGC_CHECK_LAUNCH();
     k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
-                                          pbin, prank);
+                                          pbin, prank, 0);
     FGC_CHECK_LAUNCH();
+    if (adaptive) {
+        k_cell_stat<<<148 * 4, 256, 0, s>>>(counts, grid);
+        FGC_CHECK_LAUNCH();
+        k_grid_refine<<<1, 32, 0, s>>>(grid, n, seen_target);
+        FGC_CHECK_LAUNCH();
+        k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid, 1);
+        FGC_CHECK_LAUNCH();
+        k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
+                                              pbin, prank, 1);
+        FGC_CHECK_LAUNCH();
+    }
     k_scan_tile_sums<<<scan_blocks, 256, 0, s>>>(counts, grid, blocksums);
     FGC_CHECK_LAUNCH();
     k_scan_block_sums<<<1, 1024, 0, s>>>(blocksums, grid);

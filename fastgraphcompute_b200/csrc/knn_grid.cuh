@@ -29,9 +29,14 @@ struct KnnGrid {
     uint32_t min_key[3];   // ~ordered(min) per binned coordinate (atomicMax)
     uint32_t max_key[3];   // ordered(max)
     uint32_t nonfinite;    // set when any coordinate is NaN/Inf
+    float ext[3];          // extent of the bounding box per grid dimension
+    int32_t bins_cap;      // largest cell count per row split the table can hold
+    int32_t refined;       // 1 when the density pass replaced the first grid by a finer one
+    unsigned long long sum_sq;   // sum over cells of (points in cell)^2, first grid
     // optional debug counters (filled when a search is launched with count_evals):
     // [0] distance evaluations, [1] 32-candidate steps, [2] list insertions,
-    // [3] 32-item metadata batches, [4] shells, [5] queries that scanned their whole row split
+    // [3] 32-item metadata batches, [4] shells, [5] queries that scanned their whole row split,
+    // [6] queries finished by the tile kernel, [7] eligible tiles
     unsigned long long counters[8];
 };
 
@@ -79,7 +84,7 @@ constexpr int kScanTile = 2048;  // elements per block in the 3-kernel scan
 
 // Byte offsets of the workspace sections (all 256-byte aligned).
 struct KnnWorkspace {
-    size_t header, shelltab, counts, blocksums, pbin, prank, sorig, sbin, sflag, scoords, total;
+    size_t header, shelltab, counts, blocksums, pbin, prank, sorig, sbin, sflag, done, scoords, total;
     int64_t cap_bins;   // capacity of the cell table (entries), host decision
     int nv;             // float4 per point in the sorted coordinate array
 };
@@ -89,7 +94,7 @@ inline KnnWorkspace knn_workspace_layout(int64_t n_vert, int n_coords, int64_t n
     (void)K;
     KnnWorkspace w;
     const int64_t n_events = n_rs > 1 ? n_rs - 1 : 1;
-    int64_t cap = 8 * n_vert + 64 * n_events + 1024;
+    int64_t cap = 16 * n_vert + 64 * n_events + 1024;
     if (cap > (int64_t)1 << 30) cap = (int64_t)1 << 30;
     if (cap < n_events) cap = n_events;
     w.cap_bins = cap;
@@ -104,6 +109,7 @@ inline KnnWorkspace knn_workspace_layout(int64_t n_vert, int n_coords, int64_t n
     w.sorig = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.sbin = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.sflag = off; off = align_up(off + (size_t)n_vert, 256);
+    w.done = off; off = align_up(off + (size_t)n_vert, 256);
     w.scoords = off; off = align_up(off + sizeof(float4) * (size_t)n_vert * w.nv, 256);
     w.total = off;
     return w;

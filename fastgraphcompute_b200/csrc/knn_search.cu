@@ -21,6 +21,7 @@
 // own; they never change which points are nearest, only which of several equidistant
 // points is kept.
 #include "knn_grid.cuh"
+#include "knn_tile.cuh"
 
 namespace fgc {
 
@@ -31,6 +32,7 @@ struct KnnArgs {
     const uint8_t *sflag;   // nullptr: no direction restriction
     const int *bounds;      // cell boundaries, total_bins + 1 entries
     const int32_t *shelltab;
+    const uint8_t *done;    // nullptr, or 1 where the tile kernel already wrote the row
     KnnGrid *grid;
     int64_t *out_idx;
     float *out_dist;
@@ -133,6 +135,7 @@ k_knn(const KnnArgs a)
     const int qi = blockIdx.x * kKnnWarps + wib;   // position in cell order
     KnnGrid *__restrict__ g = a.grid;
     if (qi >= a.n_vert || g->status != 0) return;
+    if (a.done && a.done[qi]) return;
 
     const int K = a.K, kn = K - 1;
     const int nc = a.n_coords;
@@ -381,8 +384,28 @@ static int launch_knn_nv(const KnnArgs &a, cudaStream_t s)
 
 }  // namespace fgc
 
+namespace fgc {
+
+template <int NV>
+static int launch_tiles(const KnnTileArgs &t, bool count, cudaStream_t s)
+{
+    const int tiles = (t.n_vert + 31) / 32;
+    const unsigned blocks = (unsigned)((tiles + kTileWarps - 1) / kTileWarps);
+    const size_t smem = sizeof(float) * (size_t)tile_smem_words(t.K - 1) * kTileWarps;
+    if (count) {
+        FGC_RETURN_IF_CUDA(cudaFuncSetAttribute(k_knn_tile<NV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_knn_tile<NV, true><<<blocks, kTileWarps * 32, smem, s>>>(t);
+    } else {
+        FGC_RETURN_IF_CUDA(cudaFuncSetAttribute(k_knn_tile<NV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_knn_tile<NV, false><<<blocks, kTileWarps * 32, smem, s>>>(t);
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace fgc
+
 extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
-                              int32_t has_direction, int32_t tf_compat, int32_t count_evals,
+                              int32_t has_direction, int32_t tf_compat, int32_t flags,
                               int64_t *out_idx, float *out_distsq, void *workspace,
                               size_t workspace_bytes, fgc_stream_t stream)
 {
@@ -392,7 +415,10 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     if (rc != FGC_OK) return rc;
     if (n_vert == 0) return FGC_OK;
     if (!out_idx || !out_distsq) return FGC_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
     char *ws = (char *)workspace;
+    const bool count = (flags & FGC_SEARCH_COUNT) != 0;
+    const bool use_tiles = (flags & FGC_SEARCH_TILES) && K >= 2 && K - 1 <= kTileMaxNeighbours;
     KnnArgs a;
     a.scoords = (const float4 *)(ws + L.scoords);
     a.sorig = (const int *)(ws + L.sorig);
@@ -400,6 +426,7 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     a.sflag = has_direction ? (const uint8_t *)(ws + L.sflag) : nullptr;
     a.bounds = (const int *)(ws + L.counts);
     a.shelltab = (const int32_t *)(ws + L.shelltab);
+    a.done = use_tiles ? (const uint8_t *)(ws + L.done) : nullptr;
     a.grid = (KnnGrid *)(ws + L.header);
     a.out_idx = out_idx;
     a.out_dist = out_distsq;
@@ -407,9 +434,20 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     a.K = K;
     a.n_coords = n_coords;
     a.tf_compat = tf_compat;
-    a.count_evals = count_evals;
-    return L.nv == 1 ? launch_knn_nv<1>(a, (cudaStream_t)stream)
-                     : launch_knn_nv<2>(a, (cudaStream_t)stream);
+    a.count_evals = count;
+    if (use_tiles) {
+        // optional first pass: tiles of 32 neighbouring queries that share their candidates; it
+        // marks the rows it completed and the pass below searches the remaining queries.
+        KnnTileArgs t;
+        t.scoords = a.scoords; t.sorig = a.sorig; t.sbin = a.sbin; t.sflag = a.sflag;
+        t.bounds = a.bounds; t.shelltab = a.shelltab; t.grid = a.grid;
+        t.out_idx = out_idx; t.out_dist = out_distsq;
+        t.done = (uint8_t *)(ws + L.done);
+        t.n_vert = (int)n_vert; t.K = K; t.n_coords = n_coords; t.tf_compat = tf_compat;
+        const int trc = L.nv == 1 ? launch_tiles<1>(t, count, s) : launch_tiles<2>(t, count, s);
+        if (trc != 0) return trc;
+    }
+    return L.nv == 1 ? launch_knn_nv<1>(a, s) : launch_knn_nv<2>(a, s);
 }
 
 extern "C" int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,

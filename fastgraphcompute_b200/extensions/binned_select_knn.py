@@ -20,6 +20,9 @@ target_occupancy = 0.0
 # call fully asynchronous but turns bad inputs (NaN, malformed row_splits) into
 # silently unwritten outputs.
 check_status = True
+# True adds the tile pass (32 neighbouring queries per warp sharing their candidates) before the
+# warp-per-query pass.  Same results; measured slower than the default on B200 so far.
+use_tiles = False
 
 
 def _raise_for_status(status):
@@ -61,7 +64,7 @@ def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=Fal
             phase_hook("search_begin")
         _cabi.check(_cabi.lib.fgc_knn_search(
             n_vert, n_coords, n_rs, K, int(direction is not None), int(bool(tf_compat)),
-            int(bool(count_evals)), _cabi.ptr(idx), _cabi.ptr(dist), _cabi.ptr(ws), nbytes, stream),
+            (1 if count_evals else 0) | (2 if use_tiles else 0), _cabi.ptr(idx), _cabi.ptr(dist), _cabi.ptr(ws), nbytes, stream),
             "fgc_knn_search")
         if phase_hook is not None:
             phase_hook("search_end")

@@ -152,23 +152,28 @@ int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,
  * mapping back to original ids and row order.  Replaces binned_select_knn_cuda_fn
  * (extensions/binned_select_knn_cuda_kernel.cu:252-384) + index_replacer + un-sort
  * scatter (extensions/binned_knn_autograd_kernel.cpp:157-195).  has_direction must say
- * whether the grid was built with a direction array.  count_evals != 0 adds the number of
- * distance evaluations to a counter in the workspace (fgc_knn_read_counters).
+ * whether the grid was built with a direction array.  flags: FGC_SEARCH_COUNT accumulates
+ * the debug counters in the workspace (fgc_knn_read_counters); FGC_SEARCH_TILES adds a
+ * first pass in which tiles of 32 neighbouring queries share their candidates (one query per
+ * lane, heaps in shared memory; same results, currently slower than the default on B200).
  */
 int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n_coords,
                        const int64_t *row_splits, int64_t n_rs, int32_t K,
                        const int64_t *direction_or_null, float target_occupancy,
                        void *workspace, size_t workspace_bytes, fgc_stream_t stream);
+#define FGC_SEARCH_COUNT 1     /* flags: accumulate the debug counters */
+#define FGC_SEARCH_TILES 2     /* flags: run the tile pass before the warp-per-query pass */
 int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
-                   int32_t has_direction, int32_t tf_compat, int32_t count_evals,
+                   int32_t has_direction, int32_t tf_compat, int32_t flags,
                    int64_t *out_idx, float *out_distsq, void *workspace,
                    size_t workspace_bytes, fgc_stream_t stream);
 
 /*
  * Diagnostics of a workspace, copied to the host (synchronises the stream): eight 64-bit
- * counters that a search launched with count_evals != 0 accumulates ([0] distance
+ * counters that a search launched with FGC_SEARCH_COUNT accumulates ([0] distance
  * evaluations, [1] 32-candidate steps, [2] list insertions, [3] metadata batches, [4] shells,
- * [5] queries that scanned their whole row split), the grid shape [3] and the cell width.
+ * [5] queries that scanned their whole row split, [6] queries finished by the tile pass,
+ * [7] eligible tiles), the grid shape [3] and the cell width.
  * Any output pointer may be NULL.  No counterpart in the reference.
  */
 int fgc_knn_read_counters(const void *workspace, uint64_t *counters_host,

@@ -1,0 +1,153 @@
+"""Full-size runs of the benchmark configurations, checked through properties that do not need
+the (slow, single-threaded) CPU oracle at that size:
+
+  * slot 0 is the point itself, neighbours stay inside their row split, no neighbour twice;
+  * stored squared distances equal the distances recomputed from the coordinates with the
+    reference's fp32 arithmetic (bit-exact);
+  * for sampled rows, an exact search over the whole row split finds the same K-th distance and
+    the same number of points strictly inside it (exact kNN up to ties at the K-th distance);
+  * the coordinate gradient is linear in the upstream gradient and sums to zero over each
+    row split (translating a whole event changes no distance).
+
+C2 (the benchmark workload) is additionally compared with the oracle at full size.
+"""
+import numpy as np
+import pytest
+import torch
+
+import parity
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+import fastgraphcompute_b200 as fgc  # noqa: E402
+from fastgraphcompute_b200 import synthetic  # noqa: E402
+from fastgraphcompute_b200.gnn_ops import GravNetOp, gravnet_aggregate  # noqa: E402
+
+DEV = "cuda:0"
+
+
+def seq_distsq(a, b):
+    """sum_d (a-b)^2, accumulated dimension by dimension in fp32, one rounding per operation."""
+    diff = a - b
+    acc = diff[..., 0] * diff[..., 0]
+    for k in range(1, diff.shape[-1]):
+        acc = acc + diff[..., k] * diff[..., k]
+    return acc
+
+
+def check_knn_properties(coords, rs, idx, dist, K, n_sample_rows=192, seed=0):
+    n = coords.shape[0]
+    rs = rs.to(torch.int64)
+    assert torch.equal(idx[:, 0], torch.arange(n, device=coords.device))
+    assert float(dist[:, 0].abs().max()) == 0.0
+    event_of = torch.searchsorted(rs, torch.arange(n, device=coords.device), right=True) - 1
+    sizes = (rs[1:] - rs[:-1])[event_of]
+    # every row split here has more than K points: no empty slots
+    assert int(sizes.min()) > K and int(idx.min()) >= 0
+    chunk = 1 << 20
+    for a in range(0, n, chunk):
+        b = min(n, a + chunk)
+        nb = idx[a:b]
+        assert torch.equal(event_of[nb.reshape(-1)].reshape(nb.shape), event_of[a:b, None].expand_as(nb))
+        srt = torch.sort(nb, dim=1).values
+        assert bool((srt[:, 1:] != srt[:, :-1]).all()), "a neighbour appears twice"
+        re = seq_distsq(coords[a:b, None, :], coords[nb])
+        assert torch.equal(re, dist[a:b]), "stored distsq differs from the recomputed one"
+    g = torch.Generator().manual_seed(seed)
+    rows = torch.randint(0, n, (n_sample_rows,), generator=g).to(coords.device)
+    for r in rows.tolist():
+        e = int(event_of[r])
+        lo, hi = int(rs[e]), int(rs[e + 1])
+        d_all = seq_distsq(coords[r][None, :], coords[lo:hi])
+        d_all[r - lo] = -1.0
+        kth = torch.kthvalue(d_all, K).values         # self counts as the first
+        mine = dist[r]
+        assert float(mine.max()) == float(kth), "K-th distance differs from the exact search"
+        # points strictly inside the K-th distance: the same number in the exact search (which
+        # holds the point itself at -1) and in the row (which holds it at 0 in slot 0)
+        assert int((d_all < kth).sum()) == int((mine < kth).sum())
+    return True
+
+
+def test_c2_full_vs_oracle_and_properties():
+    w = synthetic.c2_gaussian_mixture()
+    c = w.coords.to(DEV).requires_grad_(True)
+    idx, dist = fgc.binned_select_knn(w.K, c, w.row_splits.to(DEV))
+    oidx, odist = oracle.binned_select_knn(w.K, w.coords.numpy(), w.row_splits.numpy())
+    st = parity.assert_knn_parity(idx.cpu().numpy(), dist.detach().cpu().numpy(), oidx, odist, what="c2 full")
+    assert st["max_rel"] == 0.0
+    (dist * w.grad_distsq.to(DEV)).sum().backward()
+    og = oracle.binned_select_knn_grad(w.grad_distsq.numpy(), idx.cpu().numpy(), w.coords.numpy())
+    parity.assert_grad_close(c.grad.cpu().numpy(), og, what="c2 full grad")
+
+
+def test_c3_full_properties():
+    w = synthetic.c3_event_batch()
+    c = w.coords.to(DEV)
+    rs = w.row_splits.to(DEV)
+    idx, dist = fgc.binned_select_knn(w.K, c, rs)
+    assert idx.shape == (w.n_points, 64)
+    check_knn_properties(c, rs, idx, dist, w.K)
+
+
+def test_c5_full_properties():
+    w = synthetic.c5_skewed()
+    c = w.coords.to(DEV)
+    rs = w.row_splits.to(DEV)
+    idx, dist = fgc.binned_select_knn(w.K, c, rs)
+    assert idx.shape == (8000000, 128)
+    check_knn_properties(c, rs, idx, dist, w.K, n_sample_rows=96)
+
+
+def test_gradient_linearity_and_translation_invariance_c3_scale():
+    w = synthetic.c3_event_batch(scale=0.25)
+    rs = w.row_splits.to(DEV)
+    c = w.coords.to(DEV).requires_grad_(True)
+    idx, dist = fgc.binned_select_knn(w.K, c, rs)
+    g = torch.Generator().manual_seed(1)
+    g1 = torch.randn(dist.shape, generator=g).to(DEV)
+    g2 = torch.randn(dist.shape, generator=g).to(DEV)
+    ga = torch.autograd.grad(dist, c, g1, retain_graph=True)[0]
+    gb = torch.autograd.grad(dist, c, g2, retain_graph=True)[0]
+    gab = torch.autograd.grad(dist, c, g1 + g2)[0]
+    parity.assert_grad_close((ga + gb).cpu().numpy(), gab.cpu().numpy(), 1e-5, "linearity")
+    seg = torch.segment_reduce(gab.double(), "sum", lengths=(rs[1:] - rs[:-1]).long(), axis=0)
+    scale = float(gab.abs().mean()) * float((rs[1:] - rs[:-1]).max())
+    assert float(seg.abs().max()) <= 1e-5 * scale
+
+
+def test_c4_full_gravnet_event_independence_and_reference_aggregate():
+    gw = synthetic.c4_gravnet()
+    m = synthetic.init_gravnet_weights(
+        GravNetOp(gw.in_channels, gw.out_channels, gw.space_dimensions, gw.propagate_dimensions, gw.k)).to(DEV)
+    x = gw.x.to(DEV).requires_grad_(True)
+    rs = gw.row_splits.to(DEV)
+    out, idx, dsq, space = m(x, rs)
+    assert out.shape == (1600000, 64) and idx.shape == (1600000, 40)
+    (out ** 2).sum().backward()
+    assert bool(torch.isfinite(x.grad).all())
+    # events are independent: event 3 alone gives the same rows as inside the batch
+    lo, hi = int(rs[3]), int(rs[4])
+    out3, idx3, dsq3, _ = m(gw.x[lo:hi].to(DEV), torch.tensor([0, hi - lo], device=DEV))
+    parity.assert_knn_parity(idx3.cpu().numpy(), dsq3.detach().cpu().numpy(),
+                             (idx[lo:hi] - lo).cpu().numpy(), dsq[lo:hi].detach().cpu().numpy(), what="event 3")
+    parity.assert_grad_close(out3.detach().cpu().numpy(), out[lo:hi].detach().cpu().numpy(), 1e-5, "event 3 out")
+    # the fused aggregation against plain torch fp32 ops of the same formula (one event)
+    prop = m.propagate_transformations(x[lo:hi]).detach().requires_grad_(True)
+    d = dsq[lo:hi].detach().requires_grad_(True)
+    nb = (idx[lo:hi] - lo)
+    fmean, fmax = gravnet_aggregate(prop, nb, d)
+    gm = torch.randn_like(fmean)
+    gx = torch.randn_like(fmax)
+    ga = torch.autograd.grad([fmean, fmax], [prop, d], [gm, gx])
+    p2 = prop.detach().clone().requires_grad_(True)
+    d2 = d.detach().clone().requires_grad_(True)
+    wgt = torch.exp(-10.0 * d2)
+    gathered = fgc.select_with_default(nb, p2, 0.0) * wgt.unsqueeze(-1)
+    rmean, rmax = gathered.mean(dim=1), gathered.max(dim=1).values
+    gr = torch.autograd.grad([rmean, rmax], [p2, d2], [gm, gx])
+    parity.assert_grad_close(fmean.detach().cpu().numpy(), rmean.detach().cpu().numpy(), 1e-5, "mean")
+    parity.assert_grad_close(fmax.detach().cpu().numpy(), rmax.detach().cpu().numpy(), 1e-5, "max")
+    parity.assert_grad_close(ga[0].cpu().numpy(), gr[0].cpu().numpy(), 1e-5, "d_prop")
+    parity.assert_grad_close(ga[1].cpu().numpy(), gr[1].cpu().numpy(), 1e-5, "d_distsq")
