@@ -30,9 +30,10 @@ FGC_MAX_BIN_DIMS = 8
 FGC_MAX_K = 257
 
 # kernels launched per call (for launch accounting in benchmarks)
-KERNELS_BUILD_GRID = 12
+KERNELS_BUILD_GRID = 15
 KERNELS_SEARCH = 1
 KERNELS_KNN_BWD = 1
+KERNELS_KNN_BWD_SORTED = 7   # reverse graph (6) + gather (1)
 KERNELS_GRAVNET_FWD = 1
 KERNELS_GRAVNET_BWD = 1
 
@@ -90,6 +91,10 @@ SIGNATURES = {
     "fgc_read_status": (ctypes.c_int, [c_void_p, ctypes.POINTER(c_i32), c_void_p]),
     "fgc_binned_knn_bwd": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i32, c_i32,
                                           c_void_p, c_void_p]),
+    "fgc_reverse_graph_bytes": (c_size, [c_i64, c_i32]),
+    "fgc_build_reverse_graph": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_void_p, c_size, c_void_p]),
+    "fgc_binned_knn_bwd_sorted": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i32, c_i32,
+                                                 c_void_p, c_size, c_void_p, c_void_p]),
     "fgc_index_replacer": (ctypes.c_int, [c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_void_p]),
     "fgc_gravnet_aggregate_fwd": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i32, c_i32,
                                                  c_void_p, c_void_p, c_void_p, c_void_p]),

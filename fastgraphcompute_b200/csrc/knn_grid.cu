@@ -8,8 +8,10 @@
 //   k_histogram   cell id per point, warp-aggregated atomic histogram; the value
 //                 returned by the atomic is the point's rank inside its cell
 //   k_scan_*      exclusive scan of the histogram -> cell boundaries
-//   k_scatter     counting-sort scatter: coordinates (padded to float4), original
-//                 id, cell id and direction flag in cell order
+//   k_cell_stat / k_grid_refine   density pass: shrink the cells where the data is clustered
+//   k_fill_ids    counting-sort scatter of the original ids into cell order
+//   k_cell_sort(_big)  ids sorted inside every cell: the layout is the same on every run
+//   k_gather      coordinates (padded to float4), cell id and direction flag in cell order
 //   k_knn         one warp per query point: walks the neighbouring cells in
 //                 expanding Chebyshev shells, evaluates 32 candidates per step
 //                 (one per lane, 16-byte loads), keeps the K-1 best in registers
@@ -263,117 +265,97 @@ k_histogram(const float *__restrict__ coords, int n_vert, int n_coords,
     }
 }
 
-// --- exclusive scan of counts[0 .. total_bins] in place (three kernels) -------
-
+// Counting-sort scatter, step 1: original ids in cell order.  The position inside a cell is
+// the rank the histogram's atomic handed out, i.e. arbitrary.
 __global__ void __launch_bounds__(256)
-k_scan_tile_sums(const int *__restrict__ counts, const KnnGrid *__restrict__ g,
-                 int *__restrict__ blocksums)
-{
-    const int n = g->total_bins + 1;
-    const int base = blockIdx.x * kScanTile;
-    if (base >= n) return;
-    int s = 0;
-#pragma unroll
-    for (int k = 0; k < kScanTile / 256; k++) {
-        const int i = base + k * 256 + threadIdx.x;
-        if (i < n) s += counts[i];
-    }
-    __shared__ int ws[8];
-    s = __reduce_add_sync(FGC_FULL_MASK, s);
-    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = s;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int t = 0;
-        for (int k = 0; k < 8; k++) t += ws[k];
-        blocksums[blockIdx.x] = t;
-    }
-}
-
-// Single block: exclusive scan of the tile sums.
-__global__ void __launch_bounds__(1024)
-k_scan_block_sums(int *__restrict__ blocksums, const KnnGrid *__restrict__ g)
-{
-    const int n = (g->total_bins + 1 + kScanTile - 1) / kScanTile;
-    __shared__ int ws[32];
-    __shared__ int carry;
-    if (threadIdx.x == 0) carry = 0;
-    __syncthreads();
-    for (int base = 0; base < n; base += 1024) {
-        const int i = base + threadIdx.x;
-        const int x = i < n ? blocksums[i] : 0;
-        int incl = x;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(FGC_FULL_MASK, incl, o);
-            if ((threadIdx.x & 31) >= o) incl += t;
-        }
-        if ((threadIdx.x & 31) == 31) ws[threadIdx.x >> 5] = incl;
-        __syncthreads();
-        if (threadIdx.x < 32) {
-            int y = ws[threadIdx.x];
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int t = __shfl_up_sync(FGC_FULL_MASK, y, o);
-                if (threadIdx.x >= o) y += t;
-            }
-            ws[threadIdx.x] = y;
-        }
-        __syncthreads();
-        const int warp_off = (threadIdx.x >> 5) ? ws[(threadIdx.x >> 5) - 1] : 0;
-        const int c = carry;
-        if (i < n) blocksums[i] = c + warp_off + incl - x;
-        __syncthreads();
-        if (threadIdx.x == 1023) carry = c + warp_off + incl;
-        __syncthreads();
-    }
-}
-
-__global__ void __launch_bounds__(256)
-k_scan_apply(int *__restrict__ counts, const KnnGrid *__restrict__ g,
-             const int *__restrict__ blocksums)
-{
-    const int n = g->total_bins + 1;
-    const int base = blockIdx.x * kScanTile;
-    if (base >= n) return;
-    constexpr int PER = kScanTile / 256;
-    int x[PER];
-    int s = 0;
-    const int first = base + threadIdx.x * PER;
-#pragma unroll
-    for (int k = 0; k < PER; k++) {
-        x[k] = first + k < n ? counts[first + k] : 0;
-        s += x[k];
-    }
-    int incl = s;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(FGC_FULL_MASK, incl, o);
-        if ((threadIdx.x & 31) >= o) incl += t;
-    }
-    __shared__ int ws[8];
-    if ((threadIdx.x & 31) == 31) ws[threadIdx.x >> 5] = incl;
-    __syncthreads();
-    int off = blocksums[blockIdx.x];
-    for (int k = 0; k < (int)(threadIdx.x >> 5); k++) off += ws[k];
-    int run = off + incl - s;
-#pragma unroll
-    for (int k = 0; k < PER; k++) {
-        if (first + k < n) counts[first + k] = run;
-        run += x[k];
-    }
-}
-
-__global__ void __launch_bounds__(256)
-k_scatter(const float *__restrict__ coords, int n_vert, int n_coords, int nv,
-          const int64_t *__restrict__ direction, const KnnGrid *__restrict__ g,
-          const int *__restrict__ bounds, const int *__restrict__ pbin,
-          const int *__restrict__ prank, float4 *__restrict__ scoords, int *__restrict__ sorig,
-          int *__restrict__ sbin, uint8_t *__restrict__ sflag)
+k_fill_ids(int n_vert, const KnnGrid *__restrict__ g, const int *__restrict__ bounds,
+           const int *__restrict__ pbin, const int *__restrict__ prank, int *__restrict__ sorig)
 {
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= n_vert || g->status != 0) return;
-    const int b = pbin[v];
-    const int pos = bounds[b] + prank[v];
+    sorig[bounds[pbin[v]] + prank[v]] = v;
+}
+
+// Step 2: sort the ids inside every cell, so that the cell-ordered layout -- and with it
+// the order in which the search visits candidates, its choice among equidistant candidates
+// and the slot order of its output -- is the same on every run.  Cells of up to
+// kLaneSortMax points are sorted by one lane each (insertion sort in place); larger cells go
+// to a work list and are sorted by one CTA each (k_cell_sort_big).
+constexpr int kLaneSortMax = 12;
+
+__global__ void __launch_bounds__(256)
+k_cell_sort(KnnGrid *__restrict__ g, const int *__restrict__ bounds, int *__restrict__ sorig,
+            int *__restrict__ biglist)
+{
+    if (g->status != 0) return;
+    const int total = g->total_bins;
+    for (int cell = blockIdx.x * blockDim.x + threadIdx.x; cell < total; cell += gridDim.x * blockDim.x) {
+        const int beg = bounds[cell], len = bounds[cell + 1] - beg;
+        if (len <= 1) continue;
+        if (len > kLaneSortMax) {
+            biglist[atomicAdd(&g->n_big_cells, 1)] = cell;
+            continue;
+        }
+        int *seg = sorig + beg;
+        for (int i = 1; i < len; i++) {
+            const int key = seg[i];
+            int j = i - 1;
+            while (j >= 0 && seg[j] > key) { seg[j + 1] = seg[j]; j--; }
+            seg[j + 1] = key;
+        }
+    }
+}
+
+// One CTA per large cell: bitonic sort in its all-ascending form, in place in global memory.
+// The sequence is treated as padded to a power of two with +infinity; a compare-exchange
+// whose upper partner lies in the padding never swaps, so it is simply skipped.
+__global__ void __launch_bounds__(256)
+k_cell_sort_big(const KnnGrid *__restrict__ g, const int *__restrict__ bounds,
+                int *__restrict__ sorig, const int *__restrict__ biglist)
+{
+    if (g->status != 0) return;
+    const int n_big = g->n_big_cells;
+    for (int w = blockIdx.x; w < n_big; w += gridDim.x) {
+        const int cell = biglist[w];
+        const int beg = bounds[cell], n = bounds[cell + 1] - beg;
+        int *seg = sorig + beg;
+        int P = 1;
+        while (P < n) P <<= 1;
+        for (int k = 2; k <= P; k <<= 1) {
+            // flip: element i of a block of k against its mirror image
+            for (int t = threadIdx.x; t < P / 2; t += blockDim.x) {
+                const int half = k >> 1, blk = t / half, off = t - blk * half;
+                const int a = blk * k + off, b = blk * k + (k - 1 - off);
+                if (b < n) {
+                    const int ka = seg[a], kb = seg[b];
+                    if (ka > kb) { seg[a] = kb; seg[b] = ka; }
+                }
+            }
+            __syncthreads();
+            for (int j = k >> 2; j > 0; j >>= 1) {
+                for (int t = threadIdx.x; t < P / 2; t += blockDim.x) {
+                    const int a = 2 * j * (t / j) + (t % j), b = a + j;
+                    if (b < n) {
+                        const int ka = seg[a], kb = seg[b];
+                        if (ka > kb) { seg[a] = kb; seg[b] = ka; }
+                    }
+                }
+                __syncthreads();
+            }
+        }
+    }
+}
+
+// Step 3: everything else in cell order, gathered through the sorted ids.
+__global__ void __launch_bounds__(256)
+k_gather(const float *__restrict__ coords, int n_vert, int n_coords, int nv,
+         const int64_t *__restrict__ direction, const KnnGrid *__restrict__ g,
+         const int *__restrict__ pbin, const int *__restrict__ sorig,
+         float4 *__restrict__ scoords, int *__restrict__ sbin, uint8_t *__restrict__ sflag)
+{
+    const int pos = blockIdx.x * blockDim.x + threadIdx.x;
+    if (pos >= n_vert || g->status != 0) return;
+    const int v = sorig[pos];
     const float *row = coords + (size_t)v * n_coords;
     for (int q = 0; q < nv; q++) {
         float4 o;
@@ -383,8 +365,7 @@ k_scatter(const float *__restrict__ coords, int n_vert, int n_coords, int nv,
         o.w = 4 * q + 3 < n_coords ? __ldg(row + 4 * q + 3) : 0.f;
         scoords[(size_t)pos * nv + q] = o;
     }
-    sorig[pos] = v;
-    sbin[pos] = b;
+    sbin[pos] = pbin[v];
     if (direction) {
         const int64_t d = direction[v];
         sflag[pos] = (d >= 0 && d <= 2) ? (uint8_t)d : (uint8_t)3;
@@ -480,14 +461,20 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
                                               pbin, prank, 1);
         FGC_CHECK_LAUNCH();
     }
-    k_scan_tile_sums<<<scan_blocks, 256, 0, s>>>(counts, grid, blocksums);
+    k_scan_tile_sums<<<scan_blocks, 256, 0, s>>>(counts, &grid->total_bins, 1, blocksums);
     FGC_CHECK_LAUNCH();
-    k_scan_block_sums<<<1, 1024, 0, s>>>(blocksums, grid);
+    k_scan_block_sums<<<1, 1024, 0, s>>>(blocksums, &grid->total_bins, 1);
     FGC_CHECK_LAUNCH();
-    k_scan_apply<<<scan_blocks, 256, 0, s>>>(counts, grid, blocksums);
+    k_scan_apply<<<scan_blocks, 256, 0, s>>>(counts, &grid->total_bins, 1, blocksums);
     FGC_CHECK_LAUNCH();
-    k_scatter<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, L.nv, direction_or_null, grid, counts,
-                                        pbin, prank, scoords, sorig, sbin, sflag);
+    k_fill_ids<<<pt_blocks, 256, 0, s>>>(n, grid, counts, pbin, prank, sorig);
+    FGC_CHECK_LAUNCH();
+    k_cell_sort<<<148 * 8, 256, 0, s>>>(grid, counts, sorig, (int *)(ws + L.biglist));
+    FGC_CHECK_LAUNCH();
+    k_cell_sort_big<<<148 * 2, 256, 0, s>>>(grid, counts, sorig, (const int *)(ws + L.biglist));
+    FGC_CHECK_LAUNCH();
+    k_gather<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, L.nv, direction_or_null, grid, pbin, sorig,
+                                       scoords, sbin, sflag);
     FGC_CHECK_LAUNCH();
     return FGC_OK;
 }

@@ -7,6 +7,7 @@
 // from the reference's n_bins / max_bin_dims arguments.
 #pragma once
 #include "fgc_common.cuh"
+#include "scan.cuh"
 
 namespace fgc {
 
@@ -32,6 +33,7 @@ struct KnnGrid {
     float ext[3];          // extent of the bounding box per grid dimension
     int32_t bins_cap;      // largest cell count per row split the table can hold
     int32_t refined;       // 1 when the density pass replaced the first grid by a finer one
+    int32_t n_big_cells;   // length of the work list of cells sorted by a whole CTA
     unsigned long long sum_sq;   // sum over cells of (points in cell)^2, first grid
     // optional debug counters (filled when a search is launched with count_evals):
     // [0] distance evaluations, [1] 32-candidate steps, [2] list insertions,
@@ -80,11 +82,10 @@ __host__ __device__ inline void shell_item_decode(int d, int u, int &o0, int &o1
 constexpr size_t kGridHeaderBytes = 256;
 static_assert(sizeof(KnnGrid) <= kGridHeaderBytes, "grid header too large");
 
-constexpr int kScanTile = 2048;  // elements per block in the 3-kernel scan
 
 // Byte offsets of the workspace sections (all 256-byte aligned).
 struct KnnWorkspace {
-    size_t header, shelltab, counts, blocksums, pbin, prank, sorig, sbin, sflag, done, scoords, total;
+    size_t header, shelltab, counts, blocksums, pbin, prank, sorig, sbin, sflag, done, biglist, scoords, total;
     int64_t cap_bins;   // capacity of the cell table (entries), host decision
     int nv;             // float4 per point in the sorted coordinate array
 };
@@ -110,6 +111,7 @@ inline KnnWorkspace knn_workspace_layout(int64_t n_vert, int n_coords, int64_t n
     w.sbin = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.sflag = off; off = align_up(off + (size_t)n_vert, 256);
     w.done = off; off = align_up(off + (size_t)n_vert, 256);
+    w.biglist = off; off = align_up(off + sizeof(int32_t) * (size_t)(n_vert / 13 + 1), 256);
     w.scoords = off; off = align_up(off + sizeof(float4) * (size_t)n_vert * w.nv, 256);
     w.total = off;
     return w;
@@ -122,7 +124,7 @@ inline int check_knn_args(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_
     if (n_vert < 0 || n_rs < 1) return FGC_ERR_BAD_ARGUMENT;
     if (n_vert > 0x7fffffff || n_rs > 0x7fffffff) return FGC_ERR_TOO_LARGE;
     if (n_coords < 2) return n_coords < 1 ? FGC_ERR_BAD_ARGUMENT : FGC_ERR_UNSUPPORTED_DIM;
-    if (n_coords > 8) return FGC_ERR_UNSUPPORTED_DIM;
+    if (n_coords > FGC_MAX_KNN_DIMS) return FGC_ERR_UNSUPPORTED_DIM;
     if (K < 1 || K > FGC_MAX_K) return FGC_ERR_UNSUPPORTED_K;
     *L = knn_workspace_layout(n_vert, n_coords, n_rs, K);
     if (!workspace || workspace_bytes < L->total || ((uintptr_t)workspace & 255)) return FGC_ERR_WORKSPACE;

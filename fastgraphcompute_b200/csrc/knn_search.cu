@@ -418,7 +418,7 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     cudaStream_t s = (cudaStream_t)stream;
     char *ws = (char *)workspace;
     const bool count = (flags & FGC_SEARCH_COUNT) != 0;
-    const bool use_tiles = (flags & FGC_SEARCH_TILES) && K >= 2 && K - 1 <= kTileMaxNeighbours;
+    const bool use_tiles = (flags & FGC_SEARCH_TILES) && K >= 2 && K - 1 <= kTileMaxNeighbours && L.nv <= 2;
     KnnArgs a;
     a.scoords = (const float4 *)(ws + L.scoords);
     a.sorig = (const int *)(ws + L.sorig);
@@ -447,7 +447,10 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
         const int trc = L.nv == 1 ? launch_tiles<1>(t, count, s) : launch_tiles<2>(t, count, s);
         if (trc != 0) return trc;
     }
-    return L.nv == 1 ? launch_knn_nv<1>(a, s) : launch_knn_nv<2>(a, s);
+    if (L.nv == 1) return launch_knn_nv<1>(a, s);
+    if (L.nv == 2) return launch_knn_nv<2>(a, s);
+    if (L.nv == 3) return launch_knn_nv<3>(a, s);
+    return launch_knn_nv<4>(a, s);
 }
 
 extern "C" int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,

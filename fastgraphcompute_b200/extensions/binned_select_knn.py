@@ -23,6 +23,10 @@ check_status = True
 # True adds the tile pass (32 neighbouring queries per warp sharing their candidates) before the
 # warp-per-query pass.  Same results; measured slower than the default on B200 so far.
 use_tiles = False
+# Backward by sorted-segment reductions over a reverse neighbour graph instead of float atomics:
+# bit-identical gradients from run to run (the atomic version, like the reference's CUDA path,
+# sums in arrival order).  Falls back to the atomic kernel when N*K >= 2^31.
+deterministic_backward = False
 
 
 def _raise_for_status(status):
@@ -107,11 +111,21 @@ class _BinnedKNN(torch.autograd.Function):
         grad_dist = grad_dist.to(dtype=torch.float32).contiguous()
         n_vert, n_coords = coords.shape
         out = torch.empty_like(coords)
+        K = idx.shape[1]
         with torch.cuda.device(coords.device):
-            _cabi.check(_cabi.lib.fgc_binned_knn_bwd(
-                _cabi.ptr(grad_dist), _cabi.ptr(idx), _cabi.ptr(coords), n_vert, idx.shape[1],
-                n_coords, _cabi.ptr(out), _cabi.current_stream(coords.device)),
-                "fgc_binned_knn_bwd")
+            stream = _cabi.current_stream(coords.device)
+            rbytes = _cabi.lib.fgc_reverse_graph_bytes(n_vert, K) if deterministic_backward else 0
+            if rbytes:
+                rg = torch.empty(rbytes, dtype=torch.uint8, device=coords.device)
+                _cabi.check(_cabi.lib.fgc_build_reverse_graph(
+                    _cabi.ptr(idx), n_vert, K, _cabi.ptr(rg), rbytes, stream), "fgc_build_reverse_graph")
+                _cabi.check(_cabi.lib.fgc_binned_knn_bwd_sorted(
+                    _cabi.ptr(grad_dist), _cabi.ptr(idx), _cabi.ptr(coords), n_vert, K, n_coords,
+                    _cabi.ptr(rg), rbytes, _cabi.ptr(out), stream), "fgc_binned_knn_bwd_sorted")
+            else:
+                _cabi.check(_cabi.lib.fgc_binned_knn_bwd(
+                    _cabi.ptr(grad_dist), _cabi.ptr(idx), _cabi.ptr(coords), n_vert, K,
+                    n_coords, _cabi.ptr(out), stream), "fgc_binned_knn_bwd")
         return out, None, None, None, None
 
 

@@ -34,7 +34,7 @@ extern "C" {
 
 #define FGC_OK 0
 #define FGC_ERR_BAD_ARGUMENT (-1)   /* null pointer, negative size, ... */
-#define FGC_ERR_UNSUPPORTED_DIM (-2)/* n_coords < 2 for the kNN (the reference raises for < 2 bin dims) */
+#define FGC_ERR_UNSUPPORTED_DIM (-2)/* kNN: n_coords < 2 (the reference raises for < 2 bin dims) or > FGC_MAX_KNN_DIMS */
 #define FGC_ERR_UNSUPPORTED_K (-3)  /* K < 1 or K > FGC_MAX_K */
 #define FGC_ERR_WORKSPACE (-4)      /* workspace too small / misaligned */
 #define FGC_ERR_TOO_LARGE (-5)      /* n_vert or a bin table exceeds 2^31-1 entries */
@@ -50,6 +50,7 @@ extern "C" {
 
 #define FGC_MAX_K 257               /* self + 256 neighbours */
 #define FGC_MAX_BIN_DIMS 8          /* coordinate dimensions accepted by fgc_bin_* */
+#define FGC_MAX_KNN_DIMS 16         /* coordinate dimensions accepted by the kNN (the first 3 are binned) */
 
 typedef struct CUstream_st *fgc_stream_t; /* == cudaStream_t */
 
@@ -225,6 +226,25 @@ int fgc_read_status(const void *workspace_or_params, int32_t *status_host, fgc_s
 int fgc_binned_knn_bwd(const float *grad_distsq, const int64_t *idx, const float *coords,
                        int64_t n_vert, int32_t K, int32_t n_coords, float *out_grad_coords,
                        fgc_stream_t stream);
+
+/*
+ * Deterministic variant of the backward: sorted-segment reductions instead of float atomics.
+ *
+ * fgc_build_reverse_graph turns idx [n_vert, K] into a CSR structure that lists, for every
+ * point n, the (row, slot) pairs with idx[row, slot] == n, each segment sorted by
+ * row*K + slot (scratch: fgc_reverse_graph_bytes, caller-provided, 256-byte aligned;
+ * requires n_vert*K < 2^31).  fgc_binned_knn_bwd_sorted computes the same gradient as
+ * fgc_binned_knn_bwd by gathering over those segments in a fixed order: bit-identical from
+ * run to run, where the atomic version (like the reference's CUDA kernel,
+ * extensions/binned_select_knn_grad_cuda_kernel.cu:58-88) depends on the order in which the
+ * atomics land.  The graph depends on idx only and can be reused for several backward calls.
+ */
+size_t fgc_reverse_graph_bytes(int64_t n_vert, int32_t K);
+int fgc_build_reverse_graph(const int64_t *idx, int64_t n_vert, int32_t K, void *rgraph,
+                            size_t rgraph_bytes, fgc_stream_t stream);
+int fgc_binned_knn_bwd_sorted(const float *grad_distsq, const int64_t *idx, const float *coords,
+                              int64_t n_vert, int32_t K, int32_t n_coords, const void *rgraph,
+                              size_t rgraph_bytes, float *out_grad_coords, fgc_stream_t stream);
 
 /* ------------------------------------------------------------------------- */
 /* index_replacer                                                             */

@@ -246,12 +246,32 @@ def test_knn_edge_cases_and_errors():
     parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), oidx, odist)
 
 
-def test_knn_is_deterministic_as_a_set():
-    w = synthetic.c2_gaussian_mixture(scale=0.1)
-    c, rs = w.coords.to(DEV), w.row_splits.to(DEV)
-    i1, d1 = fgc.binned_select_knn(w.K, c, rs)
-    i2, d2 = fgc.binned_select_knn(w.K, c, rs)
-    parity.assert_knn_parity(i1.cpu().numpy(), d1.cpu().numpy(), i2.cpu().numpy(), d2.cpu().numpy())
+def test_knn_many_dimensions_vs_oracle():
+    g = torch.Generator().manual_seed(77)
+    for d, k in ((9, 12), (12, 40), (16, 7)):
+        coords = torch.randn((1500, d), generator=g)
+        rs = torch.tensor([0, 500, 1500])
+        idx, dist = fgc.binned_select_knn(k, coords.to(DEV), rs.to(DEV))
+        oidx, odist = oracle.binned_select_knn(k, coords.numpy(), rs.numpy())
+        st = parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), oidx, odist, what="D=%d" % d)
+        assert st["max_rel"] == 0.0
+    with pytest.raises(ValueError, match="dimensions"):
+        fgc.binned_select_knn(4, torch.rand((50, 17), device=DEV), torch.tensor([0, 50], device=DEV))
+
+
+def test_knn_is_bit_reproducible():
+    """Cell layout, visiting order and tie choices are fixed: two runs agree bit for bit,
+    slot order included (clustered data, data with many exact ties, direction masks)."""
+    g = torch.Generator().manual_seed(9)
+    lattice = torch.randint(0, 12, (20000, 3), generator=g).float() * 0.125
+    w = synthetic.c2_gaussian_mixture(scale=0.25)
+    w5 = synthetic.c5_skewed(scale=0.02, n_events=2)
+    for coords, rs, K in ((w.coords, w.row_splits, w.K), (lattice, torch.tensor([0, 9000, 20000]), 12),
+                          (w5.coords, w5.row_splits, 40)):
+        c, r = coords.to(DEV), rs.to(DEV)
+        i1, d1 = fgc.binned_select_knn(K, c, r)
+        i2, d2 = fgc.binned_select_knn(K, c, r)
+        assert torch.equal(i1, i2) and torch.equal(d1, d2)
 
 
 # ---------------------------------------------------------------- GravNet ----------------------
@@ -335,3 +355,47 @@ def test_knn_tile_pass_golden(golden_dir):
         parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), oidx, odist, what="tiles c2")
     finally:
         km.use_tiles = False
+
+
+def test_knn_backward_sorted_segments_is_bit_reproducible(golden_dir):
+    """The sorted-segment backward: same gradients as the oracle, identical bits on every run."""
+    import importlib
+    km = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
+    km.deterministic_backward = True
+    try:
+        for maker, scale in ((synthetic.c2_gaussian_mixture, 0.2), (synthetic.c1_two_events, 1.0)):
+            w = maker(scale=scale)
+            grads = []
+            for _ in range(3):
+                c = w.coords.to(DEV).requires_grad_(True)
+                idx, dist = fgc.binned_select_knn(w.K, c, w.row_splits.to(DEV))
+                order = torch.sort(idx, dim=1).indices      # slot order may differ between runs
+                sd = torch.gather(dist, 1, order)
+                (sd * w.grad_distsq.to(DEV)).sum().backward()
+                grads.append(c.grad.clone())
+            # the upstream gradient is attached to the rows sorted by neighbour id, so the sums
+            # have the same terms every time; only their order could differ
+            og_idx = torch.sort(idx, dim=1).values.cpu().numpy()
+            assert torch.equal(grads[0], grads[1]) and torch.equal(grads[0], grads[2])
+            og = oracle.binned_select_knn_grad(w.grad_distsq.numpy(), og_idx, w.coords.numpy())
+            parity.assert_grad_close(grads[0].cpu().numpy(), og, what=w.name + " sorted-segment grad")
+        # a hub: every point lists point 0 (in-degree 3000 > the shared-memory sort limit)
+        n, k = 3000, 4
+        g = torch.Generator().manual_seed(2)
+        coords = torch.rand((n, 3), generator=g)
+        idx = torch.stack([torch.arange(n), torch.zeros(n, dtype=torch.int64),
+                           torch.randint(0, n, (n,), generator=g), torch.full((n,), -1)], 1)
+        gd = torch.randn((n, k), generator=g)
+        from fastgraphcompute_b200 import _cabi
+        ci, cc, cg = idx.to(DEV), coords.to(DEV), gd.to(DEV)
+        rb = _cabi.lib.fgc_reverse_graph_bytes(n, k)
+        rg = torch.empty(rb, dtype=torch.uint8, device=DEV)
+        out = torch.empty_like(cc)
+        st = _cabi.current_stream(cc.device)
+        assert _cabi.lib.fgc_build_reverse_graph(_cabi.ptr(ci), n, k, _cabi.ptr(rg), rb, st) == 0
+        assert _cabi.lib.fgc_binned_knn_bwd_sorted(_cabi.ptr(cg), _cabi.ptr(ci), _cabi.ptr(cc), n, k, 3,
+                                                   _cabi.ptr(rg), rb, _cabi.ptr(out), st) == 0
+        og = oracle.binned_select_knn_grad(gd.numpy(), idx.numpy(), coords.numpy())
+        parity.assert_grad_close(out.cpu().numpy(), og, what="hub")
+    finally:
+        km.deterministic_backward = False
