@@ -9,6 +9,11 @@
 // feature channels, every neighbour row is read once (128-byte coalesced) and
 // consumed from registers.  argmax keeps the first slot that attains the max.
 //
+// `order` (optional) is a permutation of the points: warp w works on point order[w].  Given
+// the cell order of the kNN that produced idx, neighbouring warps work on neighbouring
+// points, whose neighbour rows largely coincide and are then served by L1 instead of L2.
+// Results do not depend on it.
+//
 // Backward (what autograd derives for the same lines):
 //   coef[i,k,p]   = g_mean[i,p]/K + g_max[i,p]*[k == argmax[i,p]]
 //   d_prop[n,p]  += w[i,k]*coef[i,k,p]                      n = idx[i,k] != -1
@@ -24,11 +29,12 @@ __global__ void __launch_bounds__(kGravWarps * 32)
 k_gravnet_fwd(const float *__restrict__ prop, const int64_t *__restrict__ idx,
               const float *__restrict__ distsq, int n_vert, int K, int P,
               float *__restrict__ out_mean, float *__restrict__ out_max,
-              int32_t *__restrict__ out_argmax)
+              int32_t *__restrict__ out_argmax, const int32_t *__restrict__ order)
 {
     const int lane = threadIdx.x & 31;
-    const int i = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
-    if (i >= n_vert) return;
+    const int wi = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
+    if (wi >= n_vert) return;
+    const int i = order ? __ldg(order + wi) : wi;
     const int pbase = blockIdx.y * 32 * PC + lane;
     float sum[PC], mx[PC];
     int am[PC];
@@ -76,11 +82,12 @@ k_gravnet_bwd(const float *__restrict__ prop, const int64_t *__restrict__ idx,
               const float *__restrict__ distsq, const int32_t *__restrict__ argmax,
               const float *__restrict__ g_mean, const float *__restrict__ g_max, int n_vert,
               int K, int P, float *__restrict__ d_prop, float *__restrict__ d_distsq,
-              int accumulate_dd)
+              int accumulate_dd, const int32_t *__restrict__ order)
 {
     const int lane = threadIdx.x & 31;
-    const int i = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
-    if (i >= n_vert) return;
+    const int wi = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
+    if (wi >= n_vert) return;
+    const int i = order ? __ldg(order + wi) : wi;
     const int pbase = blockIdx.y * 32 * PC + lane;
     float gm[PC], gx[PC];
     int am[PC];
@@ -128,11 +135,142 @@ k_gravnet_bwd(const float *__restrict__ prop, const int64_t *__restrict__ idx,
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Vectorised variants for P % 4 == 0 and P <= 128: a lane holds FOUR consecutive channels
+// (16-byte loads, 16-byte vector reductions), LPN = ceil(P/4) rounded up to a power of two
+// lanes cover one neighbour row and the 32/LPN lane groups of a warp work on different
+// neighbour slots at the same time.  Per neighbour the shuffles, address arithmetic and
+// compares are paid once per four channels instead of once per channel.  The groups' partial
+// sums and maxima are combined by a fixed butterfly (ties between equal maxima go to the
+// lower slot, i.e. "first slot that attains the max" is preserved).
+// ---------------------------------------------------------------------------------------
+
+template <int LPN>
+__global__ void __launch_bounds__(kGravWarps * 32)
+k_gravnet_fwd_v4(const float *__restrict__ prop, const int64_t *__restrict__ idx,
+                 const float *__restrict__ distsq, int n_vert, int K, int P,
+                 float *__restrict__ out_mean, float *__restrict__ out_max,
+                 int32_t *__restrict__ out_argmax, const int32_t *__restrict__ order)
+{
+    constexpr int G = 32 / LPN;
+    const int lane = threadIdx.x & 31;
+    const int wi = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
+    if (wi >= n_vert) return;
+    const int i = order ? __ldg(order + wi) : wi;
+    const int grp = lane / LPN, c4 = (lane % LPN) * 4;
+    const bool chan = c4 < P;
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    int am[4] = {0, 0, 0, 0};
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        const int k = k0 + lane;
+        int n_l = -1;
+        float w_l = 0.f;
+        if (k < K) {
+            const int64_t n64 = idx[(size_t)i * K + k];
+            n_l = (n64 >= 0 && n64 < n_vert) ? (int)n64 : -1;
+            w_l = expf(__fmul_rn(-10.f, distsq[(size_t)i * K + k]));
+        }
+        const int cnt = min(32, K - k0);
+        for (int kk = 0; kk < cnt; kk += G) {
+            const int ks = kk + grp;                     // this group's slot in the chunk
+            const int n = __shfl_sync(FGC_FULL_MASK, n_l, ks & 31);
+            const float w = __shfl_sync(FGC_FULL_MASK, w_l, ks & 31);
+            if (ks < cnt && chan) {
+                float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (n >= 0) x = __ldg((const float4 *)(prop + (size_t)n * P + c4));
+                const float v[4] = {__fmul_rn(x.x, w), __fmul_rn(x.y, w), __fmul_rn(x.z, w), __fmul_rn(x.w, w)};
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    sum[c] = __fadd_rn(sum[c], v[c]);
+                    if (v[c] > mx[c]) { mx[c] = v[c]; am[c] = k0 + ks; }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int off = LPN; off < 32; off <<= 1) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            sum[c] = __fadd_rn(sum[c], __shfl_xor_sync(FGC_FULL_MASK, sum[c], off));
+            const float om = __shfl_xor_sync(FGC_FULL_MASK, mx[c], off);
+            const int oa = __shfl_xor_sync(FGC_FULL_MASK, am[c], off);
+            if (om > mx[c] || (om == mx[c] && oa < am[c])) { mx[c] = om; am[c] = oa; }
+        }
+    }
+    if (grp == 0 && chan) {
+        const float kf = (float)K;
+        *(float4 *)(out_mean + (size_t)i * P + c4) =
+            make_float4(__fdiv_rn(sum[0], kf), __fdiv_rn(sum[1], kf), __fdiv_rn(sum[2], kf), __fdiv_rn(sum[3], kf));
+        *(float4 *)(out_max + (size_t)i * P + c4) = make_float4(mx[0], mx[1], mx[2], mx[3]);
+        if (out_argmax) *(int4 *)(out_argmax + (size_t)i * P + c4) = make_int4(am[0], am[1], am[2], am[3]);
+    }
+}
+
+template <int LPN>
+__global__ void __launch_bounds__(kGravWarps * 32)
+k_gravnet_bwd_v4(const float *__restrict__ prop, const int64_t *__restrict__ idx,
+                 const float *__restrict__ distsq, const int32_t *__restrict__ argmax,
+                 const float *__restrict__ g_mean, const float *__restrict__ g_max, int n_vert,
+                 int K, int P, float *__restrict__ d_prop, float *__restrict__ d_distsq,
+                 const int32_t *__restrict__ order)
+{
+    constexpr int G = 32 / LPN;
+    const int lane = threadIdx.x & 31;
+    const int wi = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
+    if (wi >= n_vert) return;
+    const int i = order ? __ldg(order + wi) : wi;
+    const int grp = lane / LPN, sub = lane % LPN, c4 = sub * 4;
+    const bool chan = c4 < P;
+    float gm[4] = {0.f, 0.f, 0.f, 0.f}, gx[4] = {0.f, 0.f, 0.f, 0.f};
+    int am[4] = {-1, -1, -1, -1};
+    if (chan) {
+        const float4 a = *(const float4 *)(g_mean + (size_t)i * P + c4);
+        const float4 b = *(const float4 *)(g_max + (size_t)i * P + c4);
+        const int4 m = *(const int4 *)(argmax + (size_t)i * P + c4);
+        const float kf = (float)K;
+        gm[0] = __fdiv_rn(a.x, kf); gm[1] = __fdiv_rn(a.y, kf); gm[2] = __fdiv_rn(a.z, kf); gm[3] = __fdiv_rn(a.w, kf);
+        gx[0] = b.x; gx[1] = b.y; gx[2] = b.z; gx[3] = b.w;
+        am[0] = m.x; am[1] = m.y; am[2] = m.z; am[3] = m.w;
+    }
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        const int k = k0 + lane;
+        int n_l = -1;
+        float w_l = 0.f;
+        if (k < K) {
+            const int64_t n64 = idx[(size_t)i * K + k];
+            n_l = (n64 >= 0 && n64 < n_vert) ? (int)n64 : -1;
+            w_l = expf(__fmul_rn(-10.f, distsq[(size_t)i * K + k]));
+        }
+        const int cnt = min(32, K - k0);
+        for (int kk = 0; kk < cnt; kk += G) {
+            const int ks = kk + grp;
+            const int n = __shfl_sync(FGC_FULL_MASK, n_l, ks & 31);
+            const float w = __shfl_sync(FGC_FULL_MASK, w_l, ks & 31);
+            const bool live = ks < cnt && n >= 0;
+            float dot = 0.f;
+            if (live && chan) {
+                const float4 x = __ldg((const float4 *)(prop + (size_t)n * P + c4));
+                float cf[4];
+#pragma unroll
+                for (int c = 0; c < 4; c++) cf[c] = gm[c] + (am[c] == k0 + ks ? gx[c] : 0.f);
+                dot = x.x * cf[0] + x.y * cf[1] + x.z * cf[2] + x.w * cf[3];
+                atomicAdd((float4 *)(d_prop + (size_t)n * P + c4),
+                          make_float4(w * cf[0], w * cf[1], w * cf[2], w * cf[3]));
+            }
+#pragma unroll
+            for (int off = LPN / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(FGC_FULL_MASK, dot, off);
+            if (sub == 0 && ks < cnt) d_distsq[(size_t)i * K + k0 + ks] = live ? -10.f * w * dot : 0.f;
+        }
+    }
+}
+
 }  // namespace fgc
 
 extern "C" int fgc_gravnet_aggregate_fwd(const float *prop, const int64_t *idx, const float *distsq,
                                          int64_t n_vert, int32_t K, int32_t P, float *out_mean,
-                                         float *out_max, int32_t *out_argmax, fgc_stream_t stream)
+                                         float *out_max, int32_t *out_argmax,
+                                         const int32_t *order_or_null, fgc_stream_t stream)
 {
     using namespace fgc;
     if (n_vert < 0 || K < 1 || P < 1) return FGC_ERR_BAD_ARGUMENT;
@@ -143,11 +281,21 @@ extern "C" int fgc_gravnet_aggregate_fwd(const float *prop, const int64_t *idx, 
     const int n = (int)n_vert;
     const int T = kGravWarps * 32;
     dim3 grid((unsigned)((n + kGravWarps - 1) / kGravWarps), 1);
-    if (P <= 32) k_gravnet_fwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax);
-    else if (P <= 64) k_gravnet_fwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax);
+    const bool vec = (P % 4 == 0) && P <= 128 && (((uintptr_t)prop | (uintptr_t)out_mean | (uintptr_t)out_max |
+                                                   (uintptr_t)out_argmax) & 15) == 0;
+    if (vec) {
+        if (P <= 16) k_gravnet_fwd_v4<4><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
+        else if (P <= 32) k_gravnet_fwd_v4<8><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
+        else if (P <= 64) k_gravnet_fwd_v4<16><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
+        else k_gravnet_fwd_v4<32><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
+        FGC_CHECK_LAUNCH();
+        return FGC_OK;
+    }
+    if (P <= 32) k_gravnet_fwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
+    else if (P <= 64) k_gravnet_fwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
     else {
         grid.y = (unsigned)((P + 127) / 128);
-        k_gravnet_fwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax);
+        k_gravnet_fwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
     }
     FGC_CHECK_LAUNCH();
     return FGC_OK;
@@ -156,7 +304,8 @@ extern "C" int fgc_gravnet_aggregate_fwd(const float *prop, const int64_t *idx, 
 extern "C" int fgc_gravnet_aggregate_bwd(const float *prop, const int64_t *idx, const float *distsq,
                                          const int32_t *argmax, const float *grad_mean,
                                          const float *grad_max, int64_t n_vert, int32_t K, int32_t P,
-                                         float *out_d_prop, float *out_d_distsq, fgc_stream_t stream)
+                                         float *out_d_prop, float *out_d_distsq,
+                                         const int32_t *order_or_null, fgc_stream_t stream)
 {
     using namespace fgc;
     if (n_vert < 0 || K < 1 || P < 1) return FGC_ERR_BAD_ARGUMENT;
@@ -169,15 +318,25 @@ extern "C" int fgc_gravnet_aggregate_bwd(const float *prop, const int64_t *idx, 
     const int T = kGravWarps * 32;
     FGC_RETURN_IF_CUDA(cudaMemsetAsync(out_d_prop, 0, sizeof(float) * (size_t)n_vert * P, s));
     dim3 grid((unsigned)((n + kGravWarps - 1) / kGravWarps), 1);
+    const bool vec = (P % 4 == 0) && P <= 128 && (((uintptr_t)prop | (uintptr_t)grad_mean | (uintptr_t)grad_max |
+                                                   (uintptr_t)argmax | (uintptr_t)out_d_prop) & 15) == 0;
+    if (vec) {
+        if (P <= 16) k_gravnet_bwd_v4<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null);
+        else if (P <= 32) k_gravnet_bwd_v4<8><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null);
+        else if (P <= 64) k_gravnet_bwd_v4<16><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null);
+        else k_gravnet_bwd_v4<32><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null);
+        FGC_CHECK_LAUNCH();
+        return FGC_OK;
+    }
     if (P <= 32)
-        k_gravnet_bwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, 0);
+        k_gravnet_bwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, 0, order_or_null);
     else if (P <= 64)
-        k_gravnet_bwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, 0);
+        k_gravnet_bwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, 0, order_or_null);
     else {
         grid.y = (unsigned)((P + 127) / 128);
         const int acc = grid.y > 1;
         if (acc) FGC_RETURN_IF_CUDA(cudaMemsetAsync(out_d_distsq, 0, sizeof(float) * (size_t)n_vert * K, s));
-        k_gravnet_bwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, acc);
+        k_gravnet_bwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, acc, order_or_null);
     }
     FGC_CHECK_LAUNCH();
     return FGC_OK;

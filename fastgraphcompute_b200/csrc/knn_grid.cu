@@ -479,6 +479,14 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
     return FGC_OK;
 }
 
+extern "C" const int32_t *fgc_knn_cell_order(const void *workspace, int64_t n_vert, int32_t n_coords,
+                                             int64_t n_rs, int32_t K)
+{
+    if (!workspace || n_vert < 0 || n_coords < 1 || n_rs < 1 || K < 1) return nullptr;
+    const fgc::KnnWorkspace L = fgc::knn_workspace_layout(n_vert, n_coords, n_rs, K);
+    return (const int32_t *)((const char *)workspace + L.sorig);
+}
+
 extern "C" int fgc_knn_read_counters(const void *workspace, uint64_t *counters_host,
                                      int32_t *grid_shape_host, float *cell_width_host,
                                      fgc_stream_t stream)

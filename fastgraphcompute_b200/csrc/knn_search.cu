@@ -446,6 +446,7 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
         t.n_vert = (int)n_vert; t.K = K; t.n_coords = n_coords; t.tf_compat = tf_compat;
         const int trc = L.nv == 1 ? launch_tiles<1>(t, count, s) : launch_tiles<2>(t, count, s);
         if (trc != 0) return trc;
+        if (flags & 4) return FGC_OK;   // timing aid: tile pass alone (rows of other queries stay unwritten)
     }
     if (L.nv == 1) return launch_knn_nv<1>(a, s);
     if (L.nv == 2) return launch_knn_nv<2>(a, s);

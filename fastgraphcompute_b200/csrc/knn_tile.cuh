@@ -27,7 +27,7 @@
 
 namespace fgc {
 
-constexpr int kTileWarps = 4;       // tiles per CTA
+constexpr int kTileWarps = 2;       // tiles per CTA
 constexpr int kTileBuf = 16;        // pending candidates per lane (merged once a lane holds more than 12)
 constexpr int kTileMaxShell = 3;    // shells a tile walks before handing leftovers over
 constexpr int kTileMaxSpan = 15;    // largest cell span (last grid dimension) of an eligible tile

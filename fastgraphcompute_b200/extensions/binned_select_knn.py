@@ -93,16 +93,28 @@ def read_counters(ws):
     return list(counters), [shape[0], shape[1], shape[2]], width.value
 
 
+def cell_order(ws, n_vert, n_coords, n_rs, K):
+    """int32 [n_vert] view into a forward's workspace: original ids in cell order (a permutation
+    that keeps spatial neighbours together; used as processing order by the GravNet kernels)."""
+    base = ws.data_ptr()
+    p = _cabi.lib.fgc_knn_cell_order(_cabi.ptr(ws), n_vert, n_coords, n_rs, K)
+    if not p:
+        raise RuntimeError("fgc_knn_cell_order: bad arguments")
+    off = p - base
+    return ws[off:off + 4 * n_vert].view(torch.int32)
+
+
 class _BinnedKNN(torch.autograd.Function):
     @staticmethod
     def forward(ctx, coords, row_splits, K, direction, tf_compat):
-        idx, dist, _ = knn_forward_raw(coords, row_splits, K, direction, tf_compat)
+        idx, dist, ws = knn_forward_raw(coords, row_splits, K, direction, tf_compat)
+        order = cell_order(ws, coords.shape[0], coords.shape[1], row_splits.numel(), K)
         ctx.save_for_backward(idx, coords)
-        ctx.mark_non_differentiable(idx)
-        return idx, dist
+        ctx.mark_non_differentiable(idx, order)
+        return idx, dist, order
 
     @staticmethod
-    def backward(ctx, grad_idx, grad_dist):
+    def backward(ctx, grad_idx, grad_dist, grad_order):
         idx, coords = ctx.saved_tensors
         if not ctx.needs_input_grad[0]:
             return None, None, None, None, None
@@ -129,28 +141,8 @@ class _BinnedKNN(torch.autograd.Function):
         return out, None, None, None, None
 
 
-def binned_select_knn(K: int, coords: torch.Tensor, row_splits: torch.Tensor,
-                      direction: Optional[torch.Tensor] = None,
-                      n_bins: Optional[torch.Tensor] = None, max_bin_dims: int = 3,
-                      torch_compatible_indices: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
-    """K nearest neighbours inside each row split.
-
-    Args:
-        K: number of neighbours including the point itself.
-        coords: [N, D] coordinates, D >= 2 (converted to float32).
-        row_splits: ragged-tensor row splits; neighbours never cross a split.
-        direction: optional [N] tensor; 0: can only be a neighbour, 1: can only have
-            neighbours, 2: neither.
-        n_bins, max_bin_dims: accepted for compatibility and validated like the
-            reference does.  They tune the reference's internal binning and do not
-            change which points are nearest; this implementation sizes its own
-            search grid from the data.
-        torch_compatible_indices: fill unused slots with the point's own index instead of -1.
-
-    Returns:
-        (indices int64 [N,K], squared distances float32 [N,K]).  Slot 0 is the point
-        itself; the order of the other slots is unspecified, as in the reference.
-    """
+def _prepare(K, coords, row_splits, direction, n_bins, max_bin_dims):
+    """Argument checks and conversions of binned_select_knn (extensions/binned_select_knn.py:36-88)."""
     _cabi.require_cuda(coords, "coords")
     if coords.dim() != 2:
         raise ValueError("coords must be [N, D]")
@@ -184,4 +176,42 @@ def binned_select_knn(K: int, coords: torch.Tensor, row_splits: torch.Tensor,
             direction = direction.detach().to(device=dev, dtype=torch.int64).contiguous()
             if direction.numel() != coords.shape[0]:
                 raise ValueError("direction must have one entry per point")
+    return K, coords, row_splits, direction
+
+
+def binned_select_knn_with_order(K, coords, row_splits, direction=None, n_bins=None, max_bin_dims=3,
+                                 torch_compatible_indices=False):
+    """binned_select_knn that also returns the cell order of its search grid: (idx, distsq,
+    order) with order int32 [N], a permutation of the points that keeps spatial neighbours
+    together.  Kernels that walk the neighbour rows (GravNet aggregation) use it as their
+    processing order for cache locality."""
+    K, coords, row_splits, direction = _prepare(K, coords, row_splits, direction, n_bins, max_bin_dims)
     return _BinnedKNN.apply(coords, row_splits, K, direction, bool(torch_compatible_indices))
+
+
+def binned_select_knn(K: int, coords: torch.Tensor, row_splits: torch.Tensor,
+                      direction: Optional[torch.Tensor] = None,
+                      n_bins: Optional[torch.Tensor] = None, max_bin_dims: int = 3,
+                      torch_compatible_indices: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """K nearest neighbours inside each row split.
+
+    Args:
+        K: number of neighbours including the point itself.
+        coords: [N, D] coordinates, 2 <= D <= 16 (converted to float32).
+        row_splits: ragged-tensor row splits; neighbours never cross a split.
+        direction: optional [N] tensor; 0: can only be a neighbour, 1: can only have
+            neighbours, 2: neither.
+        n_bins, max_bin_dims: accepted for compatibility and validated like the
+            reference does.  They tune the reference's internal binning and do not
+            change which points are nearest; this implementation sizes its own
+            search grid from the data.
+        torch_compatible_indices: fill unused slots with the point's own index instead of -1.
+
+    Returns:
+        (indices int64 [N,K], squared distances float32 [N,K]).  Slot 0 is the point
+        itself; the order of the other slots is unspecified, as in the reference (it is
+        the same on every run, though).
+    """
+    idx, dist, _ = binned_select_knn_with_order(K, coords, row_splits, direction, n_bins, max_bin_dims,
+                                                torch_compatible_indices)
+    return idx, dist

@@ -10,15 +10,17 @@ from typing import Tuple
 import torch
 
 from . import _cabi
-from .extensions.binned_select_knn import binned_select_knn
+from .extensions.binned_select_knn import binned_select_knn_with_order
 
 
 class _GravNetAggregate(torch.autograd.Function):
     """exp(-10 d^2)-weighted mean and max over the neighbour slots (gnn_ops.py:90-102)."""
 
     @staticmethod
-    def forward(ctx, propagate, neighbor_idx, distsq):
+    def forward(ctx, propagate, neighbor_idx, distsq, order):
         _cabi.require_cuda(propagate, "propagate")
+        if order is not None:
+            order = order.to(torch.int32).contiguous()
         prop = propagate.to(torch.float32).contiguous()
         idx = neighbor_idx.to(torch.int64).contiguous()
         dsq = distsq.to(torch.float32).contiguous()
@@ -30,9 +32,10 @@ class _GravNetAggregate(torch.autograd.Function):
         with torch.cuda.device(prop.device):
             _cabi.check(_cabi.lib.fgc_gravnet_aggregate_fwd(
                 _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(dsq), n_vert, K, P, _cabi.ptr(fmean),
-                _cabi.ptr(fmax), _cabi.ptr(argmax), _cabi.current_stream(prop.device)),
-                "fgc_gravnet_aggregate_fwd")
+                _cabi.ptr(fmax), _cabi.ptr(argmax), _cabi.ptr(order),
+                _cabi.current_stream(prop.device)), "fgc_gravnet_aggregate_fwd")
         ctx.save_for_backward(prop, idx, dsq, argmax)
+        ctx.order = order
         return fmean, fmax
 
     @staticmethod
@@ -48,13 +51,16 @@ class _GravNetAggregate(torch.autograd.Function):
             _cabi.check(_cabi.lib.fgc_gravnet_aggregate_bwd(
                 _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(dsq), _cabi.ptr(argmax),
                 _cabi.ptr(g_mean), _cabi.ptr(g_max), n_vert, K, P, _cabi.ptr(d_prop),
-                _cabi.ptr(d_dsq), _cabi.current_stream(prop.device)), "fgc_gravnet_aggregate_bwd")
-        return d_prop, None, d_dsq
+                _cabi.ptr(d_dsq), _cabi.ptr(ctx.order), _cabi.current_stream(prop.device)),
+                "fgc_gravnet_aggregate_bwd")
+        return d_prop, None, d_dsq, None
 
 
-def gravnet_aggregate(propagate, neighbor_idx, distsq):
-    """(mean, max) over the K neighbour slots of exp(-10*distsq)-weighted neighbour features."""
-    return _GravNetAggregate.apply(propagate, neighbor_idx, distsq)
+def gravnet_aggregate(propagate, neighbor_idx, distsq, order=None):
+    """(mean, max) over the K neighbour slots of exp(-10*distsq)-weighted neighbour features.
+
+    order: optional int32 [N] permutation used as processing order (cache locality only)."""
+    return _GravNetAggregate.apply(propagate, neighbor_idx, distsq, order)
 
 
 class GravNetOp(torch.nn.Module):
@@ -87,7 +93,7 @@ class GravNetOp(torch.nn.Module):
                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
         space = self.space_transformations(x)
         propagate = self.propagate_transformations(x)
-        neighbor_idx, distsq = binned_select_knn(self.k, space.contiguous(), row_splits)
-        fmean, fmax = gravnet_aggregate(propagate, neighbor_idx, distsq)
+        neighbor_idx, distsq, order = binned_select_knn_with_order(self.k, space.contiguous(), row_splits)
+        fmean, fmax = gravnet_aggregate(propagate, neighbor_idx, distsq, order)
         out = self.output_transformations(torch.cat([x, fmean, fmax], dim=1))
         return out, neighbor_idx, distsq, space

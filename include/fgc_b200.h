@@ -211,6 +211,15 @@ int fgc_binned_knn_fwd_static(const float *coords, int64_t n_vert, int32_t n_coo
                               int32_t *out_status, fgc_stream_t stream);
 
 /*
+ * Device pointer to the cell order inside a kNN workspace after fgc_knn_build_grid: int32
+ * [n_vert], entry p = original id of the p-th point in cell order (a permutation that keeps
+ * spatial neighbours together).  NULL on bad arguments.  No counterpart in the reference
+ * (its equivalent is the argsort at extensions/binned_knn_autograd_kernel.cpp:118-120).
+ */
+const int32_t *fgc_knn_cell_order(const void *workspace, int64_t n_vert, int32_t n_coords,
+                                  int64_t n_rs, int32_t K);
+
+/*
  * Copies the status word at the start of a workspace / fgc_bin_params to the
  * host and waits for the stream (the only synchronising call of the library).
  */
@@ -268,11 +277,14 @@ int fgc_index_replacer(const int64_t *to_be_replaced, int64_t n, const int64_t *
  * select_with_default of extensions/oc_helper.py:232-271): weights exp(-10 distsq),
  * gather of neighbour rows (-1 -> 0), mean over the K slots (divided by K) and
  * max over the K slots.  out_argmax [n_vert, P] int32 records the slot of the max
- * for the backward pass.
+ * for the backward pass.  order_or_null [n_vert] int32: optional processing order (a
+ * permutation of the points, e.g. fgc_knn_cell_order of the kNN that produced idx); it only
+ * improves cache locality, results do not depend on it.
  */
 int fgc_gravnet_aggregate_fwd(const float *prop, const int64_t *idx, const float *distsq,
                               int64_t n_vert, int32_t K, int32_t P, float *out_mean,
-                              float *out_max, int32_t *out_argmax, fgc_stream_t stream);
+                              float *out_max, int32_t *out_argmax, const int32_t *order_or_null,
+                              fgc_stream_t stream);
 
 /*
  * Backward of the aggregation (what autograd derives for gnn_ops.py:90-102).
@@ -281,7 +293,8 @@ int fgc_gravnet_aggregate_fwd(const float *prop, const int64_t *idx, const float
 int fgc_gravnet_aggregate_bwd(const float *prop, const int64_t *idx, const float *distsq,
                               const int32_t *argmax, const float *grad_mean,
                               const float *grad_max, int64_t n_vert, int32_t K, int32_t P,
-                              float *out_d_prop, float *out_d_distsq, fgc_stream_t stream);
+                              float *out_d_prop, float *out_d_distsq, const int32_t *order_or_null,
+                              fgc_stream_t stream);
 
 #ifdef __cplusplus
 }

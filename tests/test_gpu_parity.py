@@ -295,6 +295,10 @@ def test_gravnet_aggregate_vs_oracle():
         odp, odd = oracle.gravnet_aggregate_bwd(prop.numpy(), idx.numpy(), dsq.numpy(), oam, gm.numpy(), gx.numpy())
         parity.assert_grad_close(pc.grad.cpu().numpy(), odp, 1e-5, "d_prop")
         parity.assert_grad_close(dc.grad.cpu().numpy(), odd, 1e-5, "d_distsq")
+        # a processing order changes which warp handles which point, nothing else
+        order = torch.randperm(n, generator=g).to(torch.int32).to(DEV)
+        fmean2, fmax2 = gravnet_aggregate(pc.detach(), idx.to(DEV), dc.detach(), order)
+        assert torch.equal(fmean2, fmean.detach()) and torch.equal(fmax2, fmax.detach())
 
 
 def test_gravnet_module_golden(golden_dir):
