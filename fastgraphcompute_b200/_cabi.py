@@ -30,7 +30,7 @@ FGC_MAX_BIN_DIMS = 8
 FGC_MAX_K = 257
 
 # kernels launched per call (for launch accounting in benchmarks)
-KERNELS_BUILD_GRID = 15
+KERNELS_BUILD_GRID = 16
 KERNELS_SEARCH = 1
 KERNELS_KNN_BWD = 1
 KERNELS_KNN_BWD_SORTED = 7   # reverse graph (6) + gather (1)

@@ -280,7 +280,8 @@ k_fill_ids(int n_vert, const KnnGrid *__restrict__ g, const int *__restrict__ bo
 // the order in which the search visits candidates, its choice among equidistant candidates
 // and the slot order of its output -- is the same on every run.  Cells of up to
 // kLaneSortMax points are sorted by one lane each (insertion sort in place); larger cells go
-// to a work list and are sorted by one CTA each (k_cell_sort_big).
+// to a work list and are sorted by one warp (k_cell_sort_warp) or, beyond 512 points, by one
+// CTA each (k_cell_sort_big).
 constexpr int kLaneSortMax = 12;
 
 __global__ void __launch_bounds__(256)
@@ -306,7 +307,23 @@ k_cell_sort(KnnGrid *__restrict__ g, const int *__restrict__ bounds, int *__rest
     }
 }
 
-// One CTA per large cell: bitonic sort in its all-ascending form, in place in global memory.
+// One warp per cell of the work list that fits the warp-level sorts.
+__global__ void __launch_bounds__(128)
+k_cell_sort_warp(const KnnGrid *__restrict__ g, const int *__restrict__ bounds,
+                 int *__restrict__ sorig, const int *__restrict__ biglist)
+{
+    __shared__ int s_keys[4][kWarpSortMaxShared];
+    if (g->status != 0) return;
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int n_big = g->n_big_cells;
+    for (int w = blockIdx.x * 4 + wib; w < n_big; w += gridDim.x * 4) {
+        const int cell = biglist[w];
+        const int beg = bounds[cell], n = bounds[cell + 1] - beg;
+        if (n <= kWarpSortMaxShared) warp_sort_segment(sorig + beg, n, s_keys[wib], lane);
+    }
+}
+
+// One CTA per cell that is too large for a warp: bitonic sort in its all-ascending form, in place in global memory.
 // The sequence is treated as padded to a power of two with +infinity; a compare-exchange
 // whose upper partner lies in the padding never swaps, so it is simply skipped.
 __global__ void __launch_bounds__(256)
@@ -318,6 +335,7 @@ k_cell_sort_big(const KnnGrid *__restrict__ g, const int *__restrict__ bounds,
     for (int w = blockIdx.x; w < n_big; w += gridDim.x) {
         const int cell = biglist[w];
         const int beg = bounds[cell], n = bounds[cell + 1] - beg;
+        if (n <= kWarpSortMaxShared) continue;   // done by k_cell_sort_warp
         int *seg = sorig + beg;
         int P = 1;
         while (P < n) P <<= 1;
@@ -470,6 +488,8 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
     k_fill_ids<<<pt_blocks, 256, 0, s>>>(n, grid, counts, pbin, prank, sorig);
     FGC_CHECK_LAUNCH();
     k_cell_sort<<<148 * 8, 256, 0, s>>>(grid, counts, sorig, (int *)(ws + L.biglist));
+    FGC_CHECK_LAUNCH();
+    k_cell_sort_warp<<<148 * 8, 128, 0, s>>>(grid, counts, sorig, (const int *)(ws + L.biglist));
     FGC_CHECK_LAUNCH();
     k_cell_sort_big<<<148 * 2, 256, 0, s>>>(grid, counts, sorig, (const int *)(ws + L.biglist));
     FGC_CHECK_LAUNCH();

@@ -8,6 +8,7 @@
 #pragma once
 #include "fgc_common.cuh"
 #include "scan.cuh"
+#include "segsort.cuh"
 
 namespace fgc {
 

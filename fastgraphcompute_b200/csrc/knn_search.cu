@@ -43,6 +43,9 @@ struct KnnArgs {
     int count_evals;
 };
 
+// Resident CTAs per SM asked of the compiler, per list size.  The search is latency-bound
+// (dependent loads of cell boundaries and candidates), so more resident warps beat fewer
+// registers spilled to L1: measured on B200, each step up to these values was faster.
 constexpr int kKnnWarps = 8;
 constexpr uint32_t kInfBits = 0x7f800000u;
 
@@ -124,7 +127,7 @@ struct NeighbourList {
 };
 
 template <int NV, int R, bool COUNT>
-__global__ void __launch_bounds__(kKnnWarps * 32, (R <= 2 ? 5 : 3))
+__global__ void __launch_bounds__(kKnnWarps * 32, (R == 1 ? 8 : (R == 2 ? 7 : (R == 4 ? 6 : 4))))
 k_knn(const KnnArgs a)
 {
     __shared__ int s_delta[kKnnWarps][32];

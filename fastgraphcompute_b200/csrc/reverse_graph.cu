@@ -12,6 +12,7 @@
 // inside a segment -- that order is arbitrary), then every segment is sorted so that
 // nothing of the arbitrary order survives.
 #include "scan.cuh"
+#include "segsort.cuh"
 
 namespace fgc {
 
@@ -53,65 +54,18 @@ k_rev_fill(const int64_t *__restrict__ idx, int64_t total, int n_vert,
 }
 
 constexpr int kSortWarps = 4;
-constexpr int kSortMaxShared = 512;   // longest segment sorted in shared memory
 
 // One warp per segment: ascending sort of the entries (keys are distinct).
 __global__ void __launch_bounds__(kSortWarps * 32)
 k_rev_sort(const int *__restrict__ offsets, int *__restrict__ entries, int n_vert)
 {
-    __shared__ int s_keys[kSortWarps][kSortMaxShared];
+    __shared__ int s_keys[kSortWarps][kWarpSortMaxShared];
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
     const int n = blockIdx.x * kSortWarps + wib;
     if (n >= n_vert) return;
     const int beg = offsets[n], deg = offsets[n + 1] - beg;
-    if (deg <= 1) return;
-    int *seg = entries + beg;
-    if (deg <= 32) {
-        // bitonic network in registers, one key per lane
-        int key = lane < deg ? seg[lane] : 0x7fffffff;
-#pragma unroll
-        for (int k = 2; k <= 32; k <<= 1)
-#pragma unroll
-            for (int j = k >> 1; j > 0; j >>= 1) {
-                const int other = __shfl_xor_sync(FGC_FULL_MASK, key, j);
-                const bool up = (lane & k) == 0;          // ascending block
-                const bool lower = (lane & j) == 0;       // lower partner keeps the smaller key
-                key = (lower == up) ? min(key, other) : max(key, other);
-            }
-        if (lane < deg) seg[lane] = key;
-    } else if (deg <= kSortMaxShared) {
-        int *keys = s_keys[wib];
-        int P = 64;
-        while (P < deg) P <<= 1;
-        for (int t = lane; t < P; t += 32) keys[t] = t < deg ? seg[t] : 0x7fffffff;
-        __syncwarp();
-        for (int k = 2; k <= P; k <<= 1)
-            for (int j = k >> 1; j > 0; j >>= 1) {
-                for (int t = lane; t < P / 2; t += 32) {
-                    // t-th compare-exchange of this stage: partner indices a < b = a + j
-                    const int a = 2 * j * (t / j) + (t % j), b = a + j;
-                    const int ka = keys[a], kb = keys[b];
-                    const bool up = (a & k) == 0;
-                    if ((ka > kb) == up) { keys[a] = kb; keys[b] = ka; }
-                }
-                __syncwarp();
-            }
-        for (int t = lane; t < deg; t += 32) seg[t] = keys[t];
-    } else {
-        // rare hub: in-place selection sort by the warp
-        for (int p = 0; p < deg - 1; p++) {
-            int best = 0x7fffffff, where = -1;
-            for (int t = p + lane; t < deg; t += 32) {
-                const int v = seg[t];
-                if (v < best) { best = v; where = t; }
-            }
-            const int gmin = __reduce_min_sync(FGC_FULL_MASK, best);
-            const unsigned who = __ballot_sync(FGC_FULL_MASK, best == gmin);
-            if (lane == __ffs(who) - 1 && where != p) { seg[where] = seg[p]; seg[p] = gmin; }
-            __syncwarp();
-        }
-    }
+    warp_sort_segment(entries + beg, deg, s_keys[wib], lane);
 }
 
 // --- kNN backward over the reverse graph -------------------------------------------------
