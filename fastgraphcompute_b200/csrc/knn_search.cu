@@ -109,8 +109,11 @@ struct NeighbourList {
     __device__ __forceinline__ int offer(int lane, float dc, int jc)
     {
         if (__float_as_uint(dc) >= tau) return 0;
-        const unsigned holders = __ballot_sync(FGC_FULL_MASK, lmax == tau);
-        if (lane == __ffs(holders) - 1) {
+        // the first lane that holds tau takes the candidate (no find-first needed: it is the
+        // holder without a holder below it)
+        const bool holds = lmax == tau;
+        const unsigned holders = __ballot_sync(FGC_FULL_MASK, holds);
+        if (holds && (holders & lanemask_lt()) == 0) {
             bool done = false;
             uint32_t m = 0;
 #pragma unroll
