@@ -7,6 +7,7 @@ hot path behind the reference's Python entry points (fastgraphcompute/__init__.p
 CUDA tensors only; the CUDA library libfgc_b200.so must have been built
 (python fastgraphcompute_b200/build.py).
 """
+from . import torch_ops  # noqa: F401  (registers the fgc_b200 dispatcher ops)
 from .extensions.bin_by_coordinates import bin_by_coordinates
 from .extensions.binned_select_knn import binned_select_knn
 from .extensions.index_replacer import index_replacer

@@ -17,6 +17,26 @@ def bin_by_coordinates(coordinates: torch.Tensor, row_splits: torch.Tensor,
                        n_bins: Optional[torch.Tensor] = None, calc_n_per_bin: bool = True,
                        pre_normalized: bool = False, name: str = ""
                        ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Assign bins to coordinates (TorchScript-compatible front of ``fgc_b200::bin_by_coordinates``;
+    arguments, results and errors as documented at bin_by_coordinates_impl)."""
+    if bin_width is None and n_bins is None:
+        raise ValueError("Either bin_width or n_bins must be provided.")
+    if torch.jit.is_scripting():
+        return torch.ops.fgc_b200.bin_by_coordinates(coordinates, row_splits, bin_width, n_bins,
+                                                     calc_n_per_bin, pre_normalized)
+    else:
+        if torch.jit.is_tracing():
+            return torch.ops.fgc_b200.bin_by_coordinates(coordinates, row_splits, bin_width, n_bins,
+                                                         calc_n_per_bin, pre_normalized)
+        return bin_by_coordinates_impl(coordinates, row_splits, bin_width, n_bins, calc_n_per_bin,
+                                       pre_normalized, name)
+
+
+def bin_by_coordinates_impl(coordinates: torch.Tensor, row_splits: torch.Tensor,
+                            bin_width: Optional[torch.Tensor] = None,
+                            n_bins: Optional[torch.Tensor] = None, calc_n_per_bin: bool = True,
+                            pre_normalized: bool = False, name: str = ""
+                            ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """Assign bins to coordinates.
 
     Args:

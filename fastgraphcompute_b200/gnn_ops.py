@@ -5,62 +5,50 @@ returned tuple.  The three Linear layers stay torch (cuBLAS); neighbour search
 and the weighted mean/max aggregation with their backward passes run in
 libfgc_b200.so.
 """
-from typing import Tuple
+from typing import Optional, Tuple
 
 import torch
 
-from . import _cabi
+from . import torch_ops  # noqa: F401  (registers the fgc_b200 dispatcher ops)
 from .extensions.binned_select_knn import binned_select_knn_with_order
 
 
 class _GravNetAggregate(torch.autograd.Function):
-    """exp(-10 d^2)-weighted mean and max over the neighbour slots (gnn_ops.py:90-102)."""
+    """Eager-mode autograd node of the aggregation (fgc_b200::gravnet_aggregate is its
+    dispatcher twin for TorchScript and tracing)."""
 
     @staticmethod
     def forward(ctx, propagate, neighbor_idx, distsq, order):
-        _cabi.require_cuda(propagate, "propagate")
-        if order is not None:
-            order = order.to(torch.int32).contiguous()
-        prop = propagate.to(torch.float32).contiguous()
-        idx = neighbor_idx.to(torch.int64).contiguous()
-        dsq = distsq.to(torch.float32).contiguous()
-        n_vert, P = prop.shape
-        K = idx.shape[1]
-        fmean = torch.empty((n_vert, P), dtype=torch.float32, device=prop.device)
-        fmax = torch.empty_like(fmean)
-        argmax = torch.empty((n_vert, P), dtype=torch.int32, device=prop.device)
-        with torch.cuda.device(prop.device):
-            _cabi.check(_cabi.lib.fgc_gravnet_aggregate_fwd(
-                _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(dsq), n_vert, K, P, _cabi.ptr(fmean),
-                _cabi.ptr(fmax), _cabi.ptr(argmax), _cabi.ptr(order),
-                _cabi.current_stream(prop.device)), "fgc_gravnet_aggregate_fwd")
-        ctx.save_for_backward(prop, idx, dsq, argmax)
+        fmean, fmax, argmax = torch_ops.gravnet_aggregate_eager(propagate, neighbor_idx, distsq, order)
+        ctx.save_for_backward(propagate, neighbor_idx, distsq, argmax)
         ctx.order = order
         return fmean, fmax
 
     @staticmethod
     def backward(ctx, g_mean, g_max):
         prop, idx, dsq, argmax = ctx.saved_tensors
-        n_vert, P = prop.shape
-        K = idx.shape[1]
-        g_mean = (torch.zeros_like(prop) if g_mean is None else g_mean.to(torch.float32)).contiguous()
-        g_max = (torch.zeros_like(prop) if g_max is None else g_max.to(torch.float32)).contiguous()
-        d_prop = torch.empty_like(prop)
-        d_dsq = torch.empty_like(dsq)
-        with torch.cuda.device(prop.device):
-            _cabi.check(_cabi.lib.fgc_gravnet_aggregate_bwd(
-                _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(dsq), _cabi.ptr(argmax),
-                _cabi.ptr(g_mean), _cabi.ptr(g_max), n_vert, K, P, _cabi.ptr(d_prop),
-                _cabi.ptr(d_dsq), _cabi.ptr(ctx.order), _cabi.current_stream(prop.device)),
-                "fgc_gravnet_aggregate_bwd")
+        if g_mean is None:
+            g_mean = torch.zeros_like(prop, dtype=torch.float32)
+        if g_max is None:
+            g_max = torch.zeros_like(prop, dtype=torch.float32)
+        d_prop, d_dsq = torch_ops.gravnet_aggregate_backward_eager(prop, idx, dsq, argmax, g_mean, g_max, ctx.order)
         return d_prop, None, d_dsq, None
 
 
-def gravnet_aggregate(propagate, neighbor_idx, distsq, order=None):
-    """(mean, max) over the K neighbour slots of exp(-10*distsq)-weighted neighbour features.
+def gravnet_aggregate(propagate: torch.Tensor, neighbor_idx: torch.Tensor, distsq: torch.Tensor,
+                      order: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(mean, max) over the K neighbour slots of exp(-10*distsq)-weighted neighbour features
+    (gnn_ops.py:90-102 of the reference, fused; differentiable w.r.t. propagate and distsq).
 
     order: optional int32 [N] permutation used as processing order (cache locality only)."""
-    return _GravNetAggregate.apply(propagate, neighbor_idx, distsq, order)
+    if torch.jit.is_scripting():
+        fmean, fmax, _ = torch.ops.fgc_b200.gravnet_aggregate(propagate, neighbor_idx, distsq, order)
+        return fmean, fmax
+    else:
+        if torch.jit.is_tracing():
+            fmean, fmax, _ = torch.ops.fgc_b200.gravnet_aggregate(propagate, neighbor_idx, distsq, order)
+            return fmean, fmax
+        return _GravNetAggregate.apply(propagate, neighbor_idx, distsq, order)
 
 
 class GravNetOp(torch.nn.Module):

@@ -1,0 +1,244 @@
+"""Dispatcher registration of the hot-path ops (namespace ``fgc_b200``).
+
+The reference exposes its native code as dispatcher ops (``TORCH_LIBRARY`` blocks in
+extensions/binned_knn_autograd_kernel.cpp:271-277, bin_by_coordinates.cpp:143-153,
+binned_select_knn_grad.cpp:58-69, index_replacer.cpp:43-53), which is what makes its Python
+wrappers and ``GravNetOp`` usable from TorchScript (script / trace / save / load).  The ops
+below do the same for this implementation: each one unpacks tensors into device pointers and
+calls the C ABI of libfgc_b200.so; autograd is attached with ``register_autograd`` and shape
+inference with ``register_fake``.
+
+    torch.ops.fgc_b200.knn_forward(coords, row_splits, K, direction, tf_compat) -> (idx, distsq, order)
+    torch.ops.fgc_b200.knn_backward(grad_distsq, idx, coords) -> grad_coords
+    torch.ops.fgc_b200.gravnet_aggregate(prop, idx, distsq, order) -> (mean, max, argmax)
+    torch.ops.fgc_b200.gravnet_aggregate_backward(...) -> (d_prop, d_distsq)
+    torch.ops.fgc_b200.index_replacer(to_be_replaced, replacements) -> replaced
+    torch.ops.fgc_b200.bin_by_coordinates(...) -> (bin_indices, flat, n_bins, bin_width, n_per_bin)
+
+``register_reference_op_names()`` additionally publishes them under the reference's own op
+names, for scripted code that calls ``torch.ops.<reference namespace>.*`` directly.
+"""
+import ctypes
+import importlib
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _cabi
+
+_knn = importlib.import_module(__package__ + ".extensions.binned_select_knn")
+
+
+# --------------------------------------------------------------------------- kNN
+
+@torch.library.custom_op("fgc_b200::knn_forward", mutates_args=())
+def knn_forward(coords: Tensor, row_splits: Tensor, K: int, direction: Optional[Tensor],
+                tf_compat: bool) -> Tuple[Tensor, Tensor, Tensor]:
+    _cabi.require_cuda(coords, "coords")
+    coords = coords.to(torch.float32).contiguous()
+    row_splits = row_splits.to(device=coords.device, dtype=torch.int64).contiguous()
+    if direction is not None:
+        direction = direction.to(device=coords.device, dtype=torch.int64).contiguous()
+    idx, dist, ws = _knn.knn_forward_raw(coords, row_splits, int(K), direction, bool(tf_compat))
+    order = _knn.cell_order(ws, coords.shape[0], coords.shape[1], row_splits.numel(), int(K)).clone()
+    return idx, dist, order
+
+
+@knn_forward.register_fake
+def _(coords, row_splits, K, direction, tf_compat):
+    n = coords.shape[0]
+    return (coords.new_empty((n, K), dtype=torch.int64), coords.new_empty((n, K), dtype=torch.float32),
+            coords.new_empty((n,), dtype=torch.int32))
+
+
+@torch.library.custom_op("fgc_b200::knn_backward", mutates_args=())
+def knn_backward(grad_distsq: Tensor, idx: Tensor, coords: Tensor) -> Tensor:
+    _cabi.require_cuda(coords, "coords")
+    grad_distsq = grad_distsq.to(torch.float32).contiguous()
+    idx = idx.to(torch.int64).contiguous()
+    coords = coords.to(torch.float32).contiguous()
+    return _knn.knn_backward_raw(grad_distsq, idx, coords)
+
+
+@knn_backward.register_fake
+def _(grad_distsq, idx, coords):
+    return torch.empty_like(coords, dtype=torch.float32)
+
+
+def _knn_setup(ctx, inputs, output):
+    coords = inputs[0]
+    idx = output[0]
+    ctx.save_for_backward(idx, coords)
+
+
+def _knn_grad(ctx, g_idx, g_dist, g_order):
+    idx, coords = ctx.saved_tensors
+    if g_dist is None:
+        return torch.zeros_like(coords), None, None, None, None
+    return torch.ops.fgc_b200.knn_backward(g_dist, idx, coords.to(torch.float32)), None, None, None, None
+
+
+knn_forward.register_autograd(_knn_grad, setup_context=_knn_setup)
+
+
+# --------------------------------------------------------------------------- GravNet aggregation
+
+def gravnet_aggregate_eager(prop: Tensor, idx: Tensor, distsq: Tensor,
+                            order: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor]:
+    """(mean, max, argmax) straight from the library (no dispatcher round trip)."""
+    _cabi.require_cuda(prop, "propagate")
+    prop = prop.to(torch.float32).contiguous()
+    idx = idx.to(torch.int64).contiguous()
+    distsq = distsq.to(torch.float32).contiguous()
+    if order is not None:
+        order = order.to(torch.int32).contiguous()
+    n_vert, P = prop.shape
+    K = idx.shape[1]
+    fmean = torch.empty((n_vert, P), dtype=torch.float32, device=prop.device)
+    fmax = torch.empty_like(fmean)
+    argmax = torch.empty((n_vert, P), dtype=torch.int32, device=prop.device)
+    with torch.cuda.device(prop.device):
+        _cabi.check(_cabi.lib.fgc_gravnet_aggregate_fwd(
+            _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(distsq), n_vert, K, P, _cabi.ptr(fmean),
+            _cabi.ptr(fmax), _cabi.ptr(argmax), _cabi.ptr(order),
+            _cabi.current_stream(prop.device)), "fgc_gravnet_aggregate_fwd")
+    return fmean, fmax, argmax
+
+
+@torch.library.custom_op("fgc_b200::gravnet_aggregate", mutates_args=())
+def gravnet_aggregate(prop: Tensor, idx: Tensor, distsq: Tensor,
+                      order: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor]:
+    return gravnet_aggregate_eager(prop, idx, distsq, order)
+
+
+@gravnet_aggregate.register_fake
+def _(prop, idx, distsq, order):
+    return (torch.empty_like(prop, dtype=torch.float32), torch.empty_like(prop, dtype=torch.float32),
+            torch.empty_like(prop, dtype=torch.int32))
+
+
+def gravnet_aggregate_backward_eager(prop: Tensor, idx: Tensor, distsq: Tensor, argmax: Tensor,
+                                     g_mean: Tensor, g_max: Tensor,
+                                     order: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+    """(d_prop, d_distsq) straight from the library."""
+    prop = prop.to(torch.float32).contiguous()
+    idx = idx.to(torch.int64).contiguous()
+    distsq = distsq.to(torch.float32).contiguous()
+    g_mean = g_mean.to(torch.float32).contiguous()
+    g_max = g_max.to(torch.float32).contiguous()
+    n_vert, P = prop.shape
+    K = idx.shape[1]
+    d_prop = torch.empty_like(prop)
+    d_dsq = torch.empty_like(distsq)
+    with torch.cuda.device(prop.device):
+        _cabi.check(_cabi.lib.fgc_gravnet_aggregate_bwd(
+            _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(distsq), _cabi.ptr(argmax.contiguous()),
+            _cabi.ptr(g_mean), _cabi.ptr(g_max), n_vert, K, P, _cabi.ptr(d_prop), _cabi.ptr(d_dsq),
+            _cabi.ptr(order), _cabi.current_stream(prop.device)), "fgc_gravnet_aggregate_bwd")
+    return d_prop, d_dsq
+
+
+@torch.library.custom_op("fgc_b200::gravnet_aggregate_backward", mutates_args=())
+def gravnet_aggregate_backward(prop: Tensor, idx: Tensor, distsq: Tensor, argmax: Tensor,
+                               g_mean: Tensor, g_max: Tensor,
+                               order: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+    return gravnet_aggregate_backward_eager(prop, idx, distsq, argmax, g_mean, g_max, order)
+
+
+@gravnet_aggregate_backward.register_fake
+def _(prop, idx, distsq, argmax, g_mean, g_max, order):
+    return torch.empty_like(prop, dtype=torch.float32), torch.empty_like(distsq, dtype=torch.float32)
+
+
+def _agg_setup(ctx, inputs, output):
+    prop, idx, distsq, order = inputs
+    ctx.save_for_backward(prop, idx, distsq, output[2])
+    ctx.order = order
+
+
+def _agg_grad(ctx, g_mean, g_max, g_argmax):
+    prop, idx, distsq, argmax = ctx.saved_tensors
+    if g_mean is None:
+        g_mean = torch.zeros_like(prop, dtype=torch.float32)
+    if g_max is None:
+        g_max = torch.zeros_like(prop, dtype=torch.float32)
+    d_prop, d_dsq = torch.ops.fgc_b200.gravnet_aggregate_backward(prop, idx, distsq, argmax, g_mean,
+                                                                   g_max, ctx.order)
+    return d_prop, None, d_dsq, None
+
+
+gravnet_aggregate.register_autograd(_agg_grad, setup_context=_agg_setup)
+
+
+# --------------------------------------------------------------------------- index_replacer, binning
+
+@torch.library.custom_op("fgc_b200::index_replacer", mutates_args=())
+def index_replacer(to_be_replaced: Tensor, replacements: Tensor) -> Tensor:
+    from .extensions.index_replacer import index_replacer_eager
+    return index_replacer_eager(to_be_replaced, replacements)
+
+
+@index_replacer.register_fake
+def _(to_be_replaced, replacements):
+    return torch.empty_like(to_be_replaced)
+
+
+@torch.library.custom_op("fgc_b200::bin_by_coordinates", mutates_args=())
+def bin_by_coordinates(coordinates: Tensor, row_splits: Tensor, bin_width: Optional[Tensor],
+                       n_bins: Optional[Tensor], calc_n_per_bin: bool,
+                       pre_normalized: bool) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    from .extensions.bin_by_coordinates import bin_by_coordinates_impl
+    return bin_by_coordinates_impl(coordinates, row_splits, bin_width, n_bins, calc_n_per_bin,
+                                   pre_normalized, "")
+
+
+# no fake implementation: the size of n_per_bin depends on the data
+
+
+# --------------------------------------------------------------------------- reference op names
+
+_REFERENCE_LIBS = []
+
+
+def register_reference_op_names():
+    """Publish the ops under the names the reference registers, so that scripted code written
+    against ``torch.ops.fastgraphcompute_custom_ops.binned_select_knn_autograd``,
+    ``torch.ops.bin_by_coordinates.bin_by_coordinates``,
+    ``torch.ops.binned_select_knn_grad.binned_select_knn_grad`` and
+    ``torch.ops.index_replacer.index_replacer`` resolves to this implementation.  Call it
+    instead of loading the reference's binned_knn_ops.so (both in one process would define the
+    same schemas twice).  Returns the list of namespaces it registered."""
+    if _REFERENCE_LIBS:
+        return [l.ns for l in _REFERENCE_LIBS]
+
+    def knn_autograd(coords, row_splits, K, direction, n_bins, max_bin_dims, torch_compatible_indices):
+        idx, dist, _ = torch.ops.fgc_b200.knn_forward(coords, row_splits, K, direction,
+                                                      torch_compatible_indices)
+        return idx, dist
+
+    def knn_grad(grad_distances, indices, distances, coordinates):
+        return torch.ops.fgc_b200.knn_backward(grad_distances, indices, coordinates)
+
+    specs = [
+        ("fastgraphcompute_custom_ops",
+         "binned_select_knn_autograd(Tensor coords, Tensor row_splits, int K, Tensor? direction, "
+         "Tensor? n_bins, int max_bin_dims, bool torch_compatible_indices) -> (Tensor, Tensor)",
+         "binned_select_knn_autograd", knn_autograd, "CompositeImplicitAutograd"),
+        ("bin_by_coordinates",
+         "bin_by_coordinates(Tensor coordinates, Tensor row_splits, Tensor? bin_width, Tensor? n_bins, "
+         "bool calc_n_per_bin, bool pre_normalized) -> (Tensor, Tensor, Tensor, Tensor, Tensor)",
+         "bin_by_coordinates", lambda *a: torch.ops.fgc_b200.bin_by_coordinates(*a), "CompositeImplicitAutograd"),
+        ("binned_select_knn_grad",
+         "binned_select_knn_grad(Tensor grad_distances, Tensor indices, Tensor distances, Tensor coordinates) -> Tensor",
+         "binned_select_knn_grad", knn_grad, "CompositeImplicitAutograd"),
+        ("index_replacer",
+         "index_replacer(Tensor to_be_replaced, Tensor replacements) -> Tensor",
+         "index_replacer", lambda a, b: torch.ops.fgc_b200.index_replacer(a, b), "CompositeImplicitAutograd"),
+    ]
+    for ns, schema, name, fn, key in specs:
+        lib = torch.library.Library(ns, "DEF")
+        lib.define(schema)
+        lib.impl(name, fn, key)
+        _REFERENCE_LIBS.append(lib)
+    return [l.ns for l in _REFERENCE_LIBS]
