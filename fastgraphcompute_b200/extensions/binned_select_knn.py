@@ -64,19 +64,27 @@ def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=Fal
             _cabi.ptr(coords), n_vert, n_coords, _cabi.ptr(row_splits), n_rs, K,
             _cabi.ptr(direction), float(target_occupancy), _cabi.ptr(ws), nbytes, stream),
             "fgc_knn_build_grid")
+        status_host = None
+        if check_status:
+            # The status word is final once the grid is built (non-finite input and malformed
+            # row_splits are detected by its first two kernels).  Copy it out now, asynchronously,
+            # and look at it after the search has been launched: the host then waits for the
+            # short grid build only, and the GPU never idles while the host checks.
+            status_host = torch.empty(1, dtype=torch.int32, pin_memory=True)
+            status_host.copy_(ws[:4].view(torch.int32), non_blocking=True)
+            status_ready = torch.cuda.Event()
+            status_ready.record()
         if phase_hook is not None:
             phase_hook("search_begin")
         _cabi.check(_cabi.lib.fgc_knn_search(
             n_vert, n_coords, n_rs, K, int(direction is not None), int(bool(tf_compat)),
-            (1 if count_evals else 0) | (2 if use_tiles else 0), _cabi.ptr(idx), _cabi.ptr(dist), _cabi.ptr(ws), nbytes, stream),
-            "fgc_knn_search")
+            (1 if count_evals else 0) | (2 if use_tiles else 0), _cabi.ptr(idx), _cabi.ptr(dist),
+            _cabi.ptr(ws), nbytes, stream), "fgc_knn_search")
         if phase_hook is not None:
             phase_hook("search_end")
-        if check_status:
-            st = ctypes.c_int32(0)
-            _cabi.check(_cabi.lib.fgc_read_status(_cabi.ptr(ws), ctypes.byref(st), stream),
-                        "fgc_read_status")
-            _raise_for_status(st.value)
+        if status_host is not None:
+            status_ready.synchronize()
+            _raise_for_status(int(status_host.item()))
     return idx, dist, ws
 
 
