@@ -69,3 +69,15 @@ def test_select_with_default_matches_oracle():
         out = select_with_default(idx, feat, -7.0)
         assert out.dtype == feat.dtype and out.shape == (20, 5, feat.shape[1])
         assert np.array_equal(out.numpy(), oracle.select_with_default(idx.numpy(), feat.numpy(), -7.0))
+
+
+def test_row_splits_batch_round_trip():
+    import torch
+    from fastgraphcompute_b200.torch_geometric_interface import (row_splits_from_strict_batch,
+                                                                  strict_batch_from_row_splits)
+    batch = torch.tensor([0, 0, 0, 1, 1, 2, 2, 2])
+    rs = row_splits_from_strict_batch(batch)
+    assert rs.tolist() == [0, 3, 5, 8] and rs.dtype == torch.int64
+    assert torch.equal(strict_batch_from_row_splits(rs), batch)
+    assert strict_batch_from_row_splits(torch.tensor([0, 2, 2, 5], dtype=torch.int32)).tolist() == [0, 0, 2, 2, 2]
+    assert row_splits_from_strict_batch(torch.tensor([4, 4, 7])).tolist() == [0, 2, 3]
