@@ -26,6 +26,7 @@
 // grid and the stopping rule are this library's own; they never change which
 // points are nearest, only which of several equidistant points is kept.
 #include "knn_grid.cuh"
+#include "shell_table.cuh"
 
 namespace fgc {
 
@@ -93,14 +94,11 @@ k_grid_setup(KnnGrid *g, int32_t *__restrict__ shelltab, const int64_t *__restri
              int n_rs, int n_vert, int n_bin_dims, int bins_target, int bins_cap)
 {
     const int lane = threadIdx.x;
-    // shell item table for radii 0..kShellTableMaxD (all lanes)
-    for (int d = 0; d <= kShellTableMaxD; d++)
-        for (int u = lane; u < shell_items(d); u += 32) {
-            int o0, o1, zlo, zhi;
-            shell_item_decode(d, u, o0, o1, zlo, zhi);
-            shelltab[shell_table_offset(d) + u] =
-                (o0 & 0xff) | ((o1 & 0xff) << 8) | ((zlo & 0xff) << 16) | ((zhi & 0xff) << 24);
-        }
+    // shell item table for radii 0..kShellTableMaxD: copied from the generated constant table
+    // (shell_table.cuh; inside a shell the items are stored nearest first, so that the candidate
+    // stream tends to run from near to far, the K-th distance tightens early and fewer
+    // candidates have to be inserted and replaced)
+    for (int u = lane; u < kShellTableEntries; u += 32) shelltab[u] = kShellTableData[u];
     // row_splits must start at 0, end at n_vert and never decrease (all lanes)
     int bad_rs = 0;
     for (int i = 1 + lane; i < n_rs; i += 32)
