@@ -272,15 +272,35 @@ def run_b200(args):
     o_dsq = torch.empty((n, K), dtype=torch.float32).pin_memory()
     o_grad = torch.empty((n, w.coords.shape[1]), dtype=torch.float32).pin_memory()
 
+    copy_stream = torch.cuda.Stream(device=dev)
+
     def step_e2e():
+        # The way a host-side caller would drive it: inputs come from pinned host memory, results
+        # go back to pinned host memory, and the copies that nothing waits for run on a second
+        # stream (upstream gradient in while the forward runs, indices/distances out while the
+        # backward runs).  Everything is inside the timed region.
+        main = torch.cuda.current_stream(dev)
         c = h_coords.to(dev, non_blocking=True).requires_grad_(True)
         rs = h_rs.to(dev, non_blocking=True)
-        g = h_grad.to(dev, non_blocking=True)
+        copy_stream.wait_stream(main)
+        with torch.cuda.stream(copy_stream):
+            g = h_grad.to(dev, non_blocking=True)
+            g_ready = torch.cuda.Event()
+            g_ready.record(copy_stream)
         idx, dsq = fgc.binned_select_knn(K, c, rs)
+        fwd_done = torch.cuda.Event()
+        fwd_done.record(main)
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(fwd_done)
+            o_idx.copy_(idx, non_blocking=True)
+            o_dsq.copy_(dsq.detach(), non_blocking=True)
+        main.wait_event(g_ready)            # the gradient has to be on the device by now ...
+        g.record_stream(main)
         dsq.backward(g)
-        o_idx.copy_(idx, non_blocking=True)
-        o_dsq.copy_(dsq.detach(), non_blocking=True)
         o_grad.copy_(c.grad, non_blocking=True)
+        idx.record_stream(copy_stream)
+        dsq.record_stream(copy_stream)
+        main.wait_stream(copy_stream)       # ... and the step ends when every copy has landed
 
     for _ in range(3):
         step_e2e()
