@@ -7,8 +7,9 @@
 //
 // One warp per row: the lanes take the K slots (coalesced idx / grad loads), the
 // row's own term is reduced inside the warp and leaves as ONE add per
-// coordinate, the neighbour term leaves as one reduction (red.global.add.f32)
-// per slot and coordinate.
+// coordinate, the neighbour term leaves as one reduction per slot: a 16-byte
+// (D = 4) or 8-byte (D = 2) vector reduction, else one fp32 reduction per
+// coordinate.
 #include "fgc_common.cuh"
 
 namespace fgc {
@@ -19,7 +20,7 @@ template <int D>
 __global__ void __launch_bounds__(kBwdWarps * 32)
 k_knn_bwd(const float *__restrict__ grad_distsq, const int64_t *__restrict__ idx,
           const float *__restrict__ coords, int n_vert, int K, int n_coords_rt,
-          float *__restrict__ out)
+          float *__restrict__ out, int vec_ok)
 {
     const int lane = threadIdx.x & 31;
     const int i = blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
@@ -36,11 +37,20 @@ k_knn_bwd(const float *__restrict__ grad_distsq, const int64_t *__restrict__ idx
                 const int64_t n = idx[(size_t)i * K + k];
                 if (n >= 0 && n < n_vert) {
                     const float g2 = 2.f * grad_distsq[(size_t)i * K + k];
+                    float c[DM];
 #pragma unroll
                     for (int v = 0; v < DM; v++) {
-                        const float c = g2 * (__ldg(coords + (size_t)n * nc + v) - xi[v]);
-                        self[v] -= c;
-                        atomicAdd(out + (size_t)n * nc + v, c);
+                        c[v] = g2 * (__ldg(coords + (size_t)n * nc + v) - xi[v]);
+                        self[v] -= c[v];
+                    }
+                    // one vector reduction per neighbour where the row is 8 or 16 bytes wide
+                    if (D == 4 && vec_ok)
+                        atomicAdd((float4 *)(out + (size_t)n * 4), make_float4(c[0], c[1 % DM], c[2 % DM], c[3 % DM]));
+                    else if (D == 2 && vec_ok)
+                        atomicAdd((float2 *)(out + (size_t)n * 2), make_float2(c[0], c[1 % DM]));
+                    else {
+#pragma unroll
+                        for (int v = 0; v < DM; v++) atomicAdd(out + (size_t)n * nc + v, c[v]);
                     }
                 }
             }
@@ -89,11 +99,12 @@ extern "C" int fgc_binned_knn_bwd(const float *grad_distsq, const int64_t *idx, 
     const int n = (int)n_vert;
     const unsigned blocks = (unsigned)((n + kBwdWarps - 1) / kBwdWarps);
     const int T = kBwdWarps * 32;
+    const int vec_ok = ((uintptr_t)out_grad_coords & 15) == 0;
     switch (n_coords) {
-    case 2: k_knn_bwd<2><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords); break;
-    case 3: k_knn_bwd<3><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords); break;
-    case 4: k_knn_bwd<4><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords); break;
-    default: k_knn_bwd<0><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords); break;
+    case 2: k_knn_bwd<2><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok); break;
+    case 3: k_knn_bwd<3><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok); break;
+    case 4: k_knn_bwd<4><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok); break;
+    default: k_knn_bwd<0><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok); break;
     }
     FGC_CHECK_LAUNCH();
     return FGC_OK;
