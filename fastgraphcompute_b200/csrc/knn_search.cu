@@ -246,9 +246,17 @@ k_knn(const KnnArgs a)
                 return fmaxf(gp, 0.f);
             };
             long long items_done = 0;
-            for (int d = 0;; ++d) {
-                const int n_items = shell_items(d);
-                const int32_t *tab = d <= kShellTableMaxD ? a.shelltab + shell_table_offset(d) : nullptr;
+            // The walk normally starts with the centre cell and shell 1 as ONE batch of 11 items
+            // (they are adjacent in the table, centre first): a sparsely filled centre cell never
+            // ends a search, and a batch of its own would cost as much as the eleven together.
+            // A centre cell that already holds 2K points gives a tight K-th distance that prunes
+            // shell 1, so it is walked on its own then.
+            const bool merged = __ldg(a.bounds + flat + 1) - __ldg(a.bounds + flat) < 2 * K;
+            for (int d = merged ? 1 : 0;; ++d) {
+                const bool first = merged && d == 1;
+                const int n_items = first ? 1 + shell_items(1) : shell_items(d);
+                const int32_t *tab = first ? a.shelltab
+                                   : (d <= kShellTableMaxD ? a.shelltab + shell_table_offset(d) : nullptr);
                 for (int base = 0; base < n_items; base += 32) {
                     const int u = base + lane;
                     bool valid = u < n_items;
