@@ -101,6 +101,9 @@ SIGNATURES = {
     "fgc_gravnet_aggregate_bwd": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                  c_void_p, c_i64, c_i32, c_i32, c_void_p, c_void_p,
                                                  c_void_p, c_void_p]),
+    "fgc_gravnet_aggregate_bwd_sorted": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                        c_void_p, c_i64, c_i32, c_i32, c_void_p, c_size,
+                                                        c_void_p, c_void_p, c_void_p, c_void_p]),
     "fgc_knn_cell_order": (c_void_p, [c_void_p, c_i64, c_i32, c_i64, c_i32]),
 }
 

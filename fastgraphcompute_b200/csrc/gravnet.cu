@@ -19,6 +19,7 @@
 //   d_prop[n,p]  += w[i,k]*coef[i,k,p]                      n = idx[i,k] != -1
 //   d_distsq[i,k] = -10*w[i,k]*sum_p prop[n,p]*coef[i,k,p]
 #include "fgc_common.cuh"
+#include "reverse_graph.cuh"
 
 namespace fgc {
 
@@ -121,7 +122,7 @@ k_gravnet_bwd(const float *__restrict__ prop, const int64_t *__restrict__ idx,
                 if (p < P) {
                     const float coef = gm[c] + (am[c] == k0 + kk ? gx[c] : 0.f);
                     dot = fmaf(__ldg(prop + (size_t)n * P + p), coef, dot);
-                    if (coef != 0.f) atomicAdd(d_prop + (size_t)n * P + p, w * coef);
+                    if (d_prop && coef != 0.f) atomicAdd(d_prop + (size_t)n * P + p, w * coef);
                 }
             }
 #pragma unroll
@@ -255,13 +256,85 @@ k_gravnet_bwd_v4(const float *__restrict__ prop, const int64_t *__restrict__ idx
 #pragma unroll
                 for (int c = 0; c < 4; c++) cf[c] = gm[c] + (am[c] == k0 + ks ? gx[c] : 0.f);
                 dot = x.x * cf[0] + x.y * cf[1] + x.z * cf[2] + x.w * cf[3];
-                atomicAdd((float4 *)(d_prop + (size_t)n * P + c4),
-                          make_float4(w * cf[0], w * cf[1], w * cf[2], w * cf[3]));
+                if (d_prop)
+                    atomicAdd((float4 *)(d_prop + (size_t)n * P + c4),
+                              make_float4(w * cf[0], w * cf[1], w * cf[2], w * cf[3]));
             }
 #pragma unroll
             for (int off = LPN / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(FGC_FULL_MASK, dot, off);
             if (sub == 0 && ks < cnt) d_distsq[(size_t)i * K + k0 + ks] = live ? -10.f * w * dot : 0.f;
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// d_prop over the reverse neighbour graph: one warp per target row n gathers
+//   d_prop[n,:] = sum over (i,k) with idx[i,k] == n of w[i,k] * coef[i,k,:]
+// from its sorted segment, lane groups taking consecutive entries, combined by a fixed
+// butterfly.  No float atomics: the result is the same on every run.
+// ---------------------------------------------------------------------------------------
+
+template <int LPN>
+__global__ void __launch_bounds__(kGravWarps * 32)
+k_gravnet_dprop_sorted_v4(const float *__restrict__ distsq, const int32_t *__restrict__ argmax,
+                          const float *__restrict__ g_mean, const float *__restrict__ g_max,
+                          int n_vert, int K, int P, const int *__restrict__ offsets,
+                          const int *__restrict__ entries, float *__restrict__ d_prop)
+{
+    constexpr int G = 32 / LPN;
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
+    if (n >= n_vert) return;
+    const int grp = lane / LPN, c4 = (lane % LPN) * 4;
+    const bool chan = c4 < P;
+    const int beg = offsets[n], end = offsets[n + 1];
+    const float kf = (float)K;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int t0 = beg; t0 < end; t0 += G) {
+        const int t = t0 + grp;
+        if (t < end && chan) {
+            const int src = __ldg(entries + t);
+            const int i = src / K, k = src - i * K;
+            const float w = expf(__fmul_rn(-10.f, __ldg(distsq + src)));
+            const float4 a = __ldg((const float4 *)(g_mean + (size_t)i * P + c4));
+            const float4 b = __ldg((const float4 *)(g_max + (size_t)i * P + c4));
+            const int4 m = __ldg((const int4 *)(argmax + (size_t)i * P + c4));
+            acc[0] += w * (__fdiv_rn(a.x, kf) + (m.x == k ? b.x : 0.f));
+            acc[1] += w * (__fdiv_rn(a.y, kf) + (m.y == k ? b.y : 0.f));
+            acc[2] += w * (__fdiv_rn(a.z, kf) + (m.z == k ? b.z : 0.f));
+            acc[3] += w * (__fdiv_rn(a.w, kf) + (m.w == k ? b.w : 0.f));
+        }
+    }
+#pragma unroll
+    for (int off = LPN; off < 32; off <<= 1)
+#pragma unroll
+        for (int c = 0; c < 4; c++) acc[c] += __shfl_xor_sync(FGC_FULL_MASK, acc[c], off);
+    if (grp == 0 && chan)
+        *(float4 *)(d_prop + (size_t)n * P + c4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
+// any P: lanes over channels, entries one after the other
+__global__ void __launch_bounds__(kGravWarps * 32)
+k_gravnet_dprop_sorted(const float *__restrict__ distsq, const int32_t *__restrict__ argmax,
+                       const float *__restrict__ g_mean, const float *__restrict__ g_max, int n_vert,
+                       int K, int P, const int *__restrict__ offsets,
+                       const int *__restrict__ entries, float *__restrict__ d_prop)
+{
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
+    if (n >= n_vert) return;
+    const int beg = offsets[n], end = offsets[n + 1];
+    const float kf = (float)K;
+    for (int p = lane; p < P; p += 32) {
+        float acc = 0.f;
+        for (int t = beg; t < end; t++) {
+            const int src = __ldg(entries + t);
+            const int i = src / K, k = src - i * K;
+            const float w = expf(__fmul_rn(-10.f, __ldg(distsq + src)));
+            acc += w * (__fdiv_rn(__ldg(g_mean + (size_t)i * P + p), kf) +
+                        (__ldg(argmax + (size_t)i * P + p) == k ? __ldg(g_max + (size_t)i * P + p) : 0.f));
+        }
+        d_prop[(size_t)n * P + p] = acc;
     }
 }
 
@@ -337,6 +410,53 @@ extern "C" int fgc_gravnet_aggregate_bwd(const float *prop, const int64_t *idx, 
         const int acc = grid.y > 1;
         if (acc) FGC_RETURN_IF_CUDA(cudaMemsetAsync(out_d_distsq, 0, sizeof(float) * (size_t)n_vert * K, s));
         k_gravnet_bwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, acc, order_or_null);
+    }
+    FGC_CHECK_LAUNCH();
+    return FGC_OK;
+}
+
+extern "C" int fgc_gravnet_aggregate_bwd_sorted(const float *prop, const int64_t *idx,
+                                                const float *distsq, const int32_t *argmax,
+                                                const float *grad_mean, const float *grad_max,
+                                                int64_t n_vert, int32_t K, int32_t P,
+                                                const void *rgraph, size_t rgraph_bytes,
+                                                float *out_d_prop, float *out_d_distsq,
+                                                const int32_t *order_or_null, fgc_stream_t stream)
+{
+    using namespace fgc;
+    if (n_vert < 0 || K < 1 || P < 1 || P > 128) return FGC_ERR_BAD_ARGUMENT;
+    if (n_vert * (int64_t)K > 0x7fffffff) return FGC_ERR_TOO_LARGE;
+    const ReverseGraphLayout RL = reverse_graph_layout(n_vert, K);
+    if (!rgraph || rgraph_bytes < RL.total || ((uintptr_t)rgraph & 255)) return FGC_ERR_WORKSPACE;
+    if (n_vert == 0) return FGC_OK;
+    if (!prop || !idx || !distsq || !argmax || !grad_mean || !grad_max || !out_d_prop || !out_d_distsq)
+        return FGC_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int n = (int)n_vert;
+    const int T = kGravWarps * 32;
+    dim3 grid((unsigned)((n + kGravWarps - 1) / kGravWarps), 1);
+    const int *offsets = (const int *)((const char *)rgraph + RL.offsets);
+    const int *entries = (const int *)((const char *)rgraph + RL.entries);
+    const bool vec = (P % 4 == 0) && (((uintptr_t)prop | (uintptr_t)grad_mean | (uintptr_t)grad_max |
+                                       (uintptr_t)argmax | (uintptr_t)out_d_prop) & 15) == 0;
+    // d_distsq: the per-row kernel without its d_prop reductions
+    if (vec) {
+        if (P <= 16) k_gravnet_bwd_v4<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null);
+        else if (P <= 32) k_gravnet_bwd_v4<8><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null);
+        else if (P <= 64) k_gravnet_bwd_v4<16><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null);
+        else k_gravnet_bwd_v4<32><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null);
+    } else if (P <= 32) k_gravnet_bwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, 0, order_or_null);
+    else if (P <= 64) k_gravnet_bwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, 0, order_or_null);
+    else k_gravnet_bwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, 0, order_or_null);
+    FGC_CHECK_LAUNCH();
+    // d_prop: gathers over the sorted reverse segments
+    if (vec) {
+        if (P <= 16) k_gravnet_dprop_sorted_v4<4><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop);
+        else if (P <= 32) k_gravnet_dprop_sorted_v4<8><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop);
+        else if (P <= 64) k_gravnet_dprop_sorted_v4<16><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop);
+        else k_gravnet_dprop_sorted_v4<32><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop);
+    } else {
+        k_gravnet_dprop_sorted<<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop);
     }
     FGC_CHECK_LAUNCH();
     return FGC_OK;

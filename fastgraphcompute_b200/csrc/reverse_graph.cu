@@ -11,26 +11,10 @@
 // Build: count (integer atomics), exclusive scan, fill (integer atomics for the position
 // inside a segment -- that order is arbitrary), then every segment is sorted so that
 // nothing of the arbitrary order survives.
-#include "scan.cuh"
+#include "reverse_graph.cuh"
 #include "segsort.cuh"
 
 namespace fgc {
-
-struct ReverseGraphLayout {
-    size_t offsets, cursor, blocksums, entries, total;
-};
-
-inline ReverseGraphLayout reverse_graph_layout(int64_t n_vert, int K)
-{
-    ReverseGraphLayout L;
-    size_t off = 0;
-    L.offsets = off; off = align_up(off + sizeof(int32_t) * (size_t)(n_vert + 1), 256);
-    L.cursor = off; off = align_up(off + sizeof(int32_t) * (size_t)(n_vert + 1), 256);
-    L.blocksums = off; off = align_up(off + sizeof(int32_t) * (size_t)((n_vert + 1) / kScanTile + 2), 256);
-    L.entries = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert * K, 256);
-    L.total = off;
-    return L;
-}
 
 __global__ void __launch_bounds__(256)
 k_rev_count(const int64_t *__restrict__ idx, int64_t total, int n_vert, int *__restrict__ counts)

@@ -29,6 +29,12 @@ from . import _cabi
 
 _knn = importlib.import_module(__package__ + ".extensions.binned_select_knn")
 
+# GravNet aggregation backward by sorted-segment gathers over the reverse neighbour graph instead
+# of float atomics (P <= 128, N*K < 2^31): bit-identical gradients from run to run, about 3x the
+# time of the atomic kernel.  Together with binned_select_knn.deterministic_backward a whole
+# GravNetOp training step becomes reproducible.
+deterministic_gravnet_backward = False
+
 
 # --------------------------------------------------------------------------- kNN
 
@@ -131,11 +137,25 @@ def gravnet_aggregate_backward_eager(prop: Tensor, idx: Tensor, distsq: Tensor, 
     K = idx.shape[1]
     d_prop = torch.empty_like(prop)
     d_dsq = torch.empty_like(distsq)
+    argmax = argmax.contiguous()
     with torch.cuda.device(prop.device):
-        _cabi.check(_cabi.lib.fgc_gravnet_aggregate_bwd(
-            _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(distsq), _cabi.ptr(argmax.contiguous()),
-            _cabi.ptr(g_mean), _cabi.ptr(g_max), n_vert, K, P, _cabi.ptr(d_prop), _cabi.ptr(d_dsq),
-            _cabi.ptr(order), _cabi.current_stream(prop.device)), "fgc_gravnet_aggregate_bwd")
+        stream = _cabi.current_stream(prop.device)
+        rbytes = 0
+        if deterministic_gravnet_backward and P <= 128:
+            rbytes = _cabi.lib.fgc_reverse_graph_bytes(n_vert, K)
+        if rbytes:
+            rg = torch.empty(rbytes, dtype=torch.uint8, device=prop.device)
+            _cabi.check(_cabi.lib.fgc_build_reverse_graph(
+                _cabi.ptr(idx), n_vert, K, _cabi.ptr(rg), rbytes, stream), "fgc_build_reverse_graph")
+            _cabi.check(_cabi.lib.fgc_gravnet_aggregate_bwd_sorted(
+                _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(distsq), _cabi.ptr(argmax), _cabi.ptr(g_mean),
+                _cabi.ptr(g_max), n_vert, K, P, _cabi.ptr(rg), rbytes, _cabi.ptr(d_prop), _cabi.ptr(d_dsq),
+                _cabi.ptr(order), stream), "fgc_gravnet_aggregate_bwd_sorted")
+        else:
+            _cabi.check(_cabi.lib.fgc_gravnet_aggregate_bwd(
+                _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(distsq), _cabi.ptr(argmax),
+                _cabi.ptr(g_mean), _cabi.ptr(g_max), n_vert, K, P, _cabi.ptr(d_prop), _cabi.ptr(d_dsq),
+                _cabi.ptr(order), stream), "fgc_gravnet_aggregate_bwd")
     return d_prop, d_dsq
 
 

@@ -296,6 +296,19 @@ int fgc_gravnet_aggregate_bwd(const float *prop, const int64_t *idx, const float
                               float *out_d_prop, float *out_d_distsq, const int32_t *order_or_null,
                               fgc_stream_t stream);
 
+/*
+ * Deterministic variant of fgc_gravnet_aggregate_bwd (P <= 128): d_prop is gathered over the
+ * sorted segments of the reverse neighbour graph of idx (fgc_build_reverse_graph) instead of
+ * being scattered with float atomics, d_distsq as before.  Bit-identical from run to run.
+ * No counterpart in the reference (torch autograd's index_put accumulation is atomic).
+ */
+int fgc_gravnet_aggregate_bwd_sorted(const float *prop, const int64_t *idx, const float *distsq,
+                                     const int32_t *argmax, const float *grad_mean,
+                                     const float *grad_max, int64_t n_vert, int32_t K, int32_t P,
+                                     const void *rgraph, size_t rgraph_bytes, float *out_d_prop,
+                                     float *out_d_distsq, const int32_t *order_or_null,
+                                     fgc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

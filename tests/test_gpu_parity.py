@@ -246,6 +246,20 @@ def test_knn_edge_cases_and_errors():
     parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), oidx, odist)
 
 
+def test_knn_many_small_events_vs_oracle():
+    """Thousands of row splits of 0..200 points (most smaller than K): every one is searched whole."""
+    g = torch.Generator().manual_seed(31)
+    sizes = torch.randint(0, 201, (3000,), generator=g)
+    rs = torch.zeros(3001, dtype=torch.int64)
+    rs[1:] = torch.cumsum(sizes, 0)
+    n = int(rs[-1])
+    coords = torch.randn((n, 3), generator=g)
+    idx, dist = fgc.binned_select_knn(24, coords.to(DEV), rs.to(DEV))
+    oidx, odist = oracle.binned_select_knn(24, coords.numpy(), rs.numpy())
+    st = parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), oidx, odist, what="small events")
+    assert st["max_rel"] == 0.0
+
+
 def test_knn_many_dimensions_vs_oracle():
     g = torch.Generator().manual_seed(77)
     for d, k in ((9, 12), (12, 40), (16, 7)):
@@ -403,3 +417,62 @@ def test_knn_backward_sorted_segments_is_bit_reproducible(golden_dir):
         parity.assert_grad_close(out.cpu().numpy(), og, what="hub")
     finally:
         km.deterministic_backward = False
+
+
+def test_gravnet_training_step_is_bit_reproducible_with_sorted_segment_backwards():
+    """With both deterministic backward variants switched on, two identical GravNetOp training
+    steps give identical bits for the output and for every gradient; the gradients still match
+    the atomic variants within tolerance."""
+    import importlib
+    km = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
+    from fastgraphcompute_b200 import torch_ops
+    gw = synthetic.c4_gravnet(scale=0.05, n_events=3)
+
+    def step():
+        torch.manual_seed(0)
+        m = synthetic.init_gravnet_weights(
+            GravNetOp(gw.in_channels, gw.out_channels, gw.space_dimensions, gw.propagate_dimensions, gw.k)).to(DEV)
+        x = gw.x.to(DEV).requires_grad_(True)
+        out = m(x, gw.row_splits.to(DEV))[0]
+        (out ** 2).sum().backward()
+        res = {"out": out.detach(), "x": x.grad}
+        res.update({k: p.grad for k, p in m.named_parameters()})
+        return res
+
+    atomic = step()
+    km.deterministic_backward = True
+    torch_ops.deterministic_gravnet_backward = True
+    try:
+        a = step()
+        b = step()
+    finally:
+        km.deterministic_backward = False
+        torch_ops.deterministic_gravnet_backward = False
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
+    for k in a:
+        # a bias gradient can cancel to ~0: measure against the layer's weight gradient
+        ref = atomic[k.replace(".bias", ".weight")]
+        scale = float(ref.abs().max()) + 1e-30
+        assert float((a[k] - atomic[k]).abs().max()) <= 2e-5 * scale, k
+    # non-vectorised channel count as well (P = 10): sorted d_prop against the oracle
+    g = torch.Generator().manual_seed(4)
+    n, k, p = 400, 9, 10
+    prop = torch.randn((n, p), generator=g)
+    dsq = torch.rand((n, k), generator=g) * 0.2
+    idx = torch.randint(0, n, (n, k), generator=g)
+    idx[torch.rand((n, k), generator=g) < 0.1] = -1
+    gm = torch.randn((n, p), generator=g)
+    gx = torch.randn((n, p), generator=g)
+    torch_ops.deterministic_gravnet_backward = True
+    try:
+        pc = prop.to(DEV).requires_grad_(True)
+        dc = dsq.to(DEV).requires_grad_(True)
+        fmean, fmax = gravnet_aggregate(pc, idx.to(DEV), dc)
+        ((fmean * gm.to(DEV)).sum() + (fmax * gx.to(DEV)).sum()).backward()
+    finally:
+        torch_ops.deterministic_gravnet_backward = False
+    _, _, oam = oracle.gravnet_aggregate_fwd(prop.numpy(), idx.numpy(), dsq.numpy())
+    odp, odd = oracle.gravnet_aggregate_bwd(prop.numpy(), idx.numpy(), dsq.numpy(), oam, gm.numpy(), gx.numpy())
+    parity.assert_grad_close(pc.grad.cpu().numpy(), odp, 1e-5, "sorted d_prop")
+    parity.assert_grad_close(dc.grad.cpu().numpy(), odd, 1e-5, "d_distsq")
