@@ -34,11 +34,11 @@ UNIT = "points/s"
 WORKLOAD = "c2: single-event binned kNN fwd+bwd, N=200000, D=4, K=32, 50-component Gaussian mixture sigma=0.02"
 L2_FLUSH_BYTES = 256 << 20
 
-# DRAM traffic of one k_knn launch on this workload: dram__bytes_read.sum (8.56 MB) +
-# dram__bytes_write.sum (46.97 MB) of the ncu capture summarised in
+# DRAM traffic of one k_knn launch on this workload: dram__bytes_read.sum (8.54 MB) +
+# dram__bytes_write.sum (53.97 MB) of the ncu capture summarised in
 # profiles/k_knn_c2_ncu_full.md.  Below the 80 MB of algorithmic bytes because part of the
 # output is still in the 126 MB L2 when the kernel ends.
-KNN_KERNEL_DRAM_TRAFFIC_BYTES = 55523000
+KNN_KERNEL_DRAM_TRAFFIC_BYTES = 62504704
 
 
 def env_int(name, default):
@@ -59,30 +59,68 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples, time-stamped on arrival."""
+    """SM clock and throttle-reason samples during the timed region.  Reads NVML directly
+    (a few hundred samples per second, read-only queries); falls back to `nvidia-smi -lms`."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, gpu_id):
-        self.samples = []
+    def __init__(self, gpu_uuid):
+        self.samples = []          # (time, sm_mhz, reasons bitmask)
+        self.max_mhz = None
+        self._stop = False
         self.proc = None
+        self.thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByUUID(gpu_uuid)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+
+            def loop():
+                while not self._stop:
+                    try:
+                        mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                        try:
+                            rs = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                        except Exception:
+                            rs = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                        self.samples.append((time.time(), float(mhz), int(rs)))
+                    except Exception:
+                        pass
+                    time.sleep(0.004)
+
+            self.thread = threading.Thread(target=loop, daemon=True)
+            self.thread.start()
+        except Exception:
+            self._start_smi(gpu_uuid)
+
+    def _start_smi(self, gpu_id):
+        fields = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+                  "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                  "clocks_event_reasons.sw_power_cap")
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(gpu_id), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "20"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+                ["nvidia-smi", "-i", str(gpu_id), "--query-gpu=" + fields, "--format=csv,noheader,nounits",
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+
+            def read():
+                bits = (0x8, 0x40, 0x20, 0x4)
+                for line in self.proc.stdout:
+                    parts = [p.strip() for p in line.split(",")]
+                    try:
+                        mask = sum(b for b, v in zip(bits, parts[2:6]) if v.lower() == "active")
+                        self.max_mhz = float(parts[1])
+                        self.samples.append((time.time(), float(parts[0]), mask))
+                    except (ValueError, IndexError):
+                        continue
+
+            self.thread = threading.Thread(target=read, daemon=True)
             self.thread.start()
         except Exception:
             self.proc = None
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.samples.append((time.time(), line.strip()))
-
     def stop(self):
+        self._stop = True
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -91,21 +129,14 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self, t0, t1):
-        rows = []
-        for ts, line in self.samples:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 8:
-                continue
-            try:
-                rows.append((ts, float(parts[0]), float(parts[1]), parts[4:8]))
-            except ValueError:
-                continue
-        under = [r for r in rows if t0 <= r[0] <= t1 + 0.05] or rows
+        under = [r for r in self.samples if t0 <= r[0] <= t1 + 0.02] or list(self.samples)
         if not under:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = sorted({names[i] for r in under for i in range(4) if r[3][i].lower() == "active"})
-        return {"sm_mhz": statistics.median(r[1] for r in under), "sm_max_mhz": under[0][2],
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        mask = 0
+        for r in under:
+            mask |= r[2]
+        reasons = sorted(name for bit, name in self.REASONS.items() if mask & bit)
+        return {"sm_mhz": statistics.median(r[1] for r in under), "sm_max_mhz": self.max_mhz,
                 "reasons": reasons, "samples": len(under)}
 
 
@@ -397,7 +428,7 @@ def run_b200(args):
                          "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": "of " + peak_kind, "traffic": KNN_KERNEL_DRAM_TRAFFIC_BYTES,
                          "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": knn_ms_avg,
-                         "note": "not HBM-bound: ncu shows 86 % of issue slots busy, DRAM at 0.6 % "
+                         "note": "not HBM-bound: ncu shows 82 % of issue slots busy, DRAM at 0.8 % "
                                  "(profiles/k_knn_c2_ncu_full.md)"},
             "roofline_fp32": {"note": "the search is bound by CUDA-core issue, not by HBM: distance evaluations x 3*D flops",
                               "distance_evals_per_launch": n_evals, "evals_per_query": n_evals / n,
