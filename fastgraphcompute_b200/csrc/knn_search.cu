@@ -74,7 +74,8 @@ __device__ __forceinline__ float dist_sq(const float4 (&q)[NV], const float4 (&c
 // largest stored distance, compared through the bit pattern (monotone for non-negative
 // floats), so while a slot is empty tau is +inf and every candidate goes to the first
 // empty slot; afterwards a candidate replaces the first slot that holds tau iff its
-// distance is strictly smaller.  Slots fill in slot order, so empty slots are a suffix.
+// distance is strictly smaller.  With R >= 2 slots fill in slot order (empty slots are a
+// suffix, which the bulk placement relies on); with R == 1 any empty slot may be taken.
 template <int R>
 struct NeighbourList {
     float d[R];
@@ -176,6 +177,18 @@ k_knn(const KnnArgs a)
         unsigned m = __ballot_sync(FGC_FULL_MASK, __float_as_uint(dc) < list.tau);
         if (m == 0) return;
         const int npass = __popc(m);
+        if (R == 1 && list.tau == kInfBits) {
+            // While the list has empty slots any of them may take a passing candidate: a lane
+            // whose own slot is empty keeps its own candidate, with no warp-wide insertion.
+            // What is left (lanes whose slot is taken or not part of the list) goes one by one.
+            const bool take = (m >> lane & 1) && __float_as_uint(list.d[0]) == kInfBits;
+            if (take) { list.d[0] = dc; list.id[0] = j; list.lmax = __float_as_uint(dc); }
+            const unsigned tm = __ballot_sync(FGC_FULL_MASK, take);
+            list.filled += __popc(tm);
+            list.tau = __reduce_max_sync(FGC_FULL_MASK, list.lmax);
+            if (COUNT) cnt_ins += __popc(tm);
+            m &= ~tm;
+        }
         if (R >= 2 && list.filled + npass <= kn) {
             // all passing candidates fit into empty slots (tau is +inf here): place them in
             // one go through shared memory instead of one warp-wide insertion each (pays
@@ -353,13 +366,27 @@ k_knn(const KnnArgs a)
     // epilogue: original ids, original row position
     if (lane == 0) { out_i[0] = orig_q; out_d[0] = 0.f; }
     const int64_t pad = a.tf_compat ? (int64_t)orig_q : (int64_t)-1;
+    if (R == 1) {
+        // occupied slots first, empty ones after them (with one slot per lane the list fills
+        // in no particular slot order)
+        const bool valid = lane < kn;
+        const bool filled = valid && __float_as_uint(list.d[0]) < kInfBits && list.id[0] >= 0;
+        const unsigned fm = __ballot_sync(FGC_FULL_MASK, filled);
+        const unsigned em = __ballot_sync(FGC_FULL_MASK, valid && !filled);
+        const int s = filled ? __popc(fm & lanemask_lt()) : __popc(fm) + __popc(em & lanemask_lt());
+        if (valid) {
+            out_i[1 + s] = filled ? (int64_t)__ldg(a.sorig + list.id[0]) : pad;
+            out_d[1 + s] = filled ? list.d[0] : 0.f;
+        }
+    } else {
 #pragma unroll
-    for (int r = 0; r < R; r++) {
-        const int s = lane * R + r;
-        if (s < kn) {
-            const bool filled = __float_as_uint(list.d[r]) < kInfBits && list.id[r] >= 0;
-            out_i[1 + s] = filled ? (int64_t)__ldg(a.sorig + list.id[r]) : pad;
-            out_d[1 + s] = filled ? list.d[r] : 0.f;
+        for (int r = 0; r < R; r++) {
+            const int s = lane * R + r;
+            if (s < kn) {
+                const bool filled = __float_as_uint(list.d[r]) < kInfBits && list.id[r] >= 0;
+                out_i[1 + s] = filled ? (int64_t)__ldg(a.sorig + list.id[r]) : pad;
+                out_d[1 + s] = filled ? list.d[r] : 0.f;
+            }
         }
     }
     if (COUNT) {
