@@ -30,7 +30,8 @@ FGC_MAX_BIN_DIMS = 8
 FGC_MAX_K = 257
 
 # kernels launched per call (for launch accounting in benchmarks)
-KERNELS_BUILD_GRID = 16
+KERNELS_BUILD_GRID = 13
+KERNELS_PUBLISH_STATUS = 1   # the wrapper's status check after the grid build
 KERNELS_SEARCH = 1
 KERNELS_KNN_BWD = 1
 KERNELS_KNN_BWD_SORTED = 7   # reverse graph (6) + gather (1)
@@ -89,6 +90,7 @@ SIGNATURES = {
                                                  c_void_p, c_i32, c_float, c_void_p, c_void_p,
                                                  c_void_p, c_void_p]),
     "fgc_read_status": (ctypes.c_int, [c_void_p, ctypes.POINTER(c_i32), c_void_p]),
+    "fgc_publish_status": (ctypes.c_int, [c_void_p, c_void_p, c_void_p]),
     "fgc_binned_knn_bwd": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i32, c_i32,
                                           c_void_p, c_void_p]),
     "fgc_reverse_graph_bytes": (c_size, [c_i64, c_i32]),

@@ -8,10 +8,11 @@
 //   k_histogram   cell id per point, warp-aggregated atomic histogram; the value
 //                 returned by the atomic is the point's rank inside its cell
 //   k_scan_*      exclusive scan of the histogram -> cell boundaries
-//   k_cell_stat / k_grid_refine   density pass: shrink the cells where the data is clustered
-//   k_fill_ids    counting-sort scatter of the original ids into cell order
-//   k_cell_sort(_big)  ids sorted inside every cell: the layout is the same on every run
-//   k_gather      coordinates (padded to float4), cell id and direction flag in cell order
+//   k_cell_stat_refine   density pass: shrink the cells where the data is clustered
+//   k_fill_ids    counting-sort scatter of the original ids into cell order (arbitrary inside a cell)
+//   k_rank_place  ids in ascending order inside every cell (the layout is the same on every
+//                 run); coordinates (padded to float4), cell id and direction flag in that order
+//   k_sort_large_cells  the same for the few cells too crowded for ranking
 //   k_knn         one warp per query point: walks the neighbouring cells in
 //                 expanding Chebyshev shells, evaluates 32 candidates per step
 //                 (one per lane, 16-byte loads), keeps the K-1 best in registers
@@ -90,15 +91,10 @@ __device__ inline void fit_shape(const float (&ext)[3], double wd, int bins_cap,
 // One thread.  Chooses the cell width so that a row split of average size gets
 // about bins_target cells, bounded by bins_cap cells per row split.
 __global__ void __launch_bounds__(32)
-k_grid_setup(KnnGrid *g, int32_t *__restrict__ shelltab, const int64_t *__restrict__ row_splits,
+k_grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits,
              int n_rs, int n_vert, int n_bin_dims, int bins_target, int bins_cap)
 {
     const int lane = threadIdx.x;
-    // shell item table for radii 0..kShellTableMaxD: copied from the generated constant table
-    // (shell_table.cuh; inside a shell the items are stored nearest first, so that the candidate
-    // stream tends to run from near to far, the K-th distance tightens early and fewer
-    // candidates have to be inserted and replaced)
-    for (int u = lane; u < kShellTableEntries; u += 32) shelltab[u] = kShellTableData[u];
     // row_splits must start at 0, end at n_vert and never decrease (all lanes)
     int bad_rs = 0;
     for (int i = 1 + lane; i < n_rs; i += 32)
@@ -164,24 +160,9 @@ k_grid_setup(KnnGrid *g, int32_t *__restrict__ shelltab, const int64_t *__restri
 // point sees in its own cell; when it is well above the wanted value the grid is rebuilt
 // with cells shrunk by the cube root of the ratio (occupancy scales with the cell volume
 // where the density is locally smooth).
-__global__ void __launch_bounds__(256) k_cell_stat(const int *__restrict__ counts, KnnGrid *g)
+__device__ void grid_refine(KnnGrid *g, unsigned long long sum_sq, int n_vert, float seen_target)
 {
-    if (g->status != 0) return;
-    const int n = g->total_bins;
-    unsigned long long s = 0;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        const unsigned long long c = (unsigned long long)counts[i];
-        s += c * c;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FGC_FULL_MASK, s, o);
-    if ((threadIdx.x & 31) == 0 && s) atomicAdd(&g->sum_sq, s);
-}
-
-__global__ void k_grid_refine(KnnGrid *g, int n_vert, float seen_target)
-{
-    if (threadIdx.x != 0 || blockIdx.x != 0 || g->status != 0) return;
-    const double seen = (double)g->sum_sq / (double)(n_vert > 0 ? n_vert : 1);
+    const double seen = (double)sum_sq / (double)(n_vert > 0 ? n_vert : 1);
     if (!(seen > 1.5 * (double)seen_target)) return;
     int nz = 0;
     float ext[3], ext_max = 0.f;
@@ -209,6 +190,32 @@ __global__ void k_grid_refine(KnnGrid *g, int n_vert, float seen_target)
     g->inv_w = __fdiv_rn(1.0f, w);
     g->slack = 4e-6f * fmaxf(ext_max, w);
     g->refined = 1;
+}
+
+// Every CTA adds its share of sum_c c^2; the CTA that finishes last (a ticket counter, no
+// waiting) decides about the finer grid.
+__global__ void __launch_bounds__(256)
+k_cell_stat_refine(const int *__restrict__ counts, KnnGrid *g, int n_vert, float seen_target)
+{
+    if (g->status != 0) return;
+    const int n = g->total_bins;
+    unsigned long long s = 0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const unsigned long long c = (unsigned long long)counts[i];
+        s += c * c;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FGC_FULL_MASK, s, o);
+    if ((threadIdx.x & 31) == 0 && s) { atomicAdd(&g->sum_sq, s); __threadfence(); }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const int ticket = atomicAdd(&g->stat_blocks_done, 1);
+        if (ticket == (int)gridDim.x - 1) {
+            __threadfence();
+            grid_refine(g, atomicAdd(&g->sum_sq, 0ull), n_vert, seen_target);
+        }
+    }
 }
 
 __global__ void __launch_bounds__(256)
@@ -267,73 +274,108 @@ k_histogram(const float *__restrict__ coords, int n_vert, int n_coords,
 // the rank the histogram's atomic handed out, i.e. arbitrary.
 __global__ void __launch_bounds__(256)
 k_fill_ids(int n_vert, const KnnGrid *__restrict__ g, const int *__restrict__ bounds,
-           const int *__restrict__ pbin, const int *__restrict__ prank, int *__restrict__ sorig)
+           const int *__restrict__ pbin, const int *__restrict__ prank, int *__restrict__ stmp)
 {
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= n_vert || g->status != 0) return;
-    sorig[bounds[pbin[v]] + prank[v]] = v;
+    stmp[bounds[pbin[v]] + prank[v]] = v;
 }
 
-// Step 2: sort the ids inside every cell, so that the cell-ordered layout -- and with it
-// the order in which the search visits candidates, its choice among equidistant candidates
-// and the slot order of its output -- is the same on every run.  Cells of up to
-// kLaneSortMax points are sorted by one lane each (insertion sort in place); larger cells go
-// to a work list and are sorted by one warp (k_cell_sort_warp) or, beyond 512 points, by one
-// CTA each (k_cell_sort_big).
-constexpr int kLaneSortMax = 12;
-
-__global__ void __launch_bounds__(256)
-k_cell_sort(KnnGrid *__restrict__ g, const int *__restrict__ bounds, int *__restrict__ sorig,
-            int *__restrict__ biglist)
+// Everything that is kept per point in cell order: original id, coordinates padded to
+// float4, cell id, direction flag.
+__device__ __forceinline__ void place_point(int pos, int v, int bin, const float *__restrict__ coords,
+                                            int n_coords, int nv, const int64_t *__restrict__ direction,
+                                            int *__restrict__ sorig, float4 *__restrict__ scoords,
+                                            int *__restrict__ sbin, uint8_t *__restrict__ sflag)
 {
-    if (g->status != 0) return;
-    const int total = g->total_bins;
-    for (int cell = blockIdx.x * blockDim.x + threadIdx.x; cell < total; cell += gridDim.x * blockDim.x) {
-        const int beg = bounds[cell], len = bounds[cell + 1] - beg;
-        if (len <= 1) continue;
-        if (len > kLaneSortMax) {
-            biglist[atomicAdd(&g->n_big_cells, 1)] = cell;
-            continue;
-        }
-        int *seg = sorig + beg;
-        for (int i = 1; i < len; i++) {
-            const int key = seg[i];
-            int j = i - 1;
-            while (j >= 0 && seg[j] > key) { seg[j + 1] = seg[j]; j--; }
-            seg[j + 1] = key;
+    const float *row = coords + (size_t)v * n_coords;
+    for (int q = 0; q < nv; q++) {
+        float4 o;
+        o.x = 4 * q + 0 < n_coords ? __ldg(row + 4 * q + 0) : 0.f;
+        o.y = 4 * q + 1 < n_coords ? __ldg(row + 4 * q + 1) : 0.f;
+        o.z = 4 * q + 2 < n_coords ? __ldg(row + 4 * q + 2) : 0.f;
+        o.w = 4 * q + 3 < n_coords ? __ldg(row + 4 * q + 3) : 0.f;
+        scoords[(size_t)pos * nv + q] = o;
+    }
+    sorig[pos] = v;
+    sbin[pos] = bin;
+    if (direction) {
+        const int64_t d = direction[v];
+        sflag[pos] = (d >= 0 && d <= 2) ? (uint8_t)d : (uint8_t)3;
+    }
+}
+
+// Step 2: the ids inside every cell in ascending order, so that the cell-ordered layout --
+// and with it the order in which the search visits candidates, its choice among equidistant
+// candidates and the slot order of its output -- is the same on every run.  One thread per
+// point: in a cell of up to kRankMax points the point's place is the number of smaller ids in
+// the cell (read from the unordered list of step 1), and everything kept in cell order is
+// written there at once.  Points of larger cells keep their arbitrary place for now and
+// the cell goes to a work list (k_sort_large_cells).
+__global__ void __launch_bounds__(256)
+k_rank_place(const float *__restrict__ coords, int n_vert, int n_coords, int nv,
+             const int64_t *__restrict__ direction, KnnGrid *__restrict__ g,
+             const int *__restrict__ bounds, const int *__restrict__ pbin,
+             const int *__restrict__ prank, const int *__restrict__ stmp,
+             int *__restrict__ sorig, float4 *__restrict__ scoords, int *__restrict__ sbin,
+             uint8_t *__restrict__ sflag, int *__restrict__ biglist, int *__restrict__ hugelist)
+{
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= n_vert || g->status != 0) return;
+    const int bin = pbin[v];
+    const int beg = bounds[bin], len = bounds[bin + 1] - beg;
+    if (len <= kRankMax) {
+        int rank = 0;
+        for (int t = 0; t < len; t++) rank += stmp[beg + t] < v ? 1 : 0;
+        place_point(beg + rank, v, bin, coords, n_coords, nv, direction, sorig, scoords, sbin, sflag);
+    } else {
+        const int r = prank[v];
+        sorig[beg + r] = v;
+        if (r == 0) {
+            if (len <= kWarpSortMaxShared) biglist[atomicAdd(&g->n_big_cells, 1)] = bin;
+            else hugelist[atomicAdd(&g->n_huge_cells, 1)] = bin;
         }
     }
 }
 
-// One warp per cell of the work list that fits the warp-level sorts.
-__global__ void __launch_bounds__(128)
-k_cell_sort_warp(const KnnGrid *__restrict__ g, const int *__restrict__ bounds,
-                 int *__restrict__ sorig, const int *__restrict__ biglist)
-{
-    __shared__ int s_keys[4][kWarpSortMaxShared];
-    if (g->status != 0) return;
-    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-    const int n_big = g->n_big_cells;
-    for (int w = blockIdx.x * 4 + wib; w < n_big; w += gridDim.x * 4) {
-        const int cell = biglist[w];
-        const int beg = bounds[cell], n = bounds[cell + 1] - beg;
-        if (n <= kWarpSortMaxShared) warp_sort_segment(sorig + beg, n, s_keys[wib], lane);
-    }
-}
+// Step 3: the cells of the work lists.  The first n_warp_blocks CTAs take the cells that one
+// warp can sort (in registers / shared memory), the remaining CTAs take the cells beyond
+// kWarpSortMaxShared points, one CTA per cell: bitonic sort in its all-ascending form, in
+// place in global memory (the sequence is treated as padded to a power of two with
+// +infinity; a compare-exchange whose upper partner lies in the padding never swaps, so it
+// is simply skipped).  After the sort the same warp / CTA places the cell's points.
+constexpr int kSortWarps = 4;
 
-// One CTA per cell that is too large for a warp: bitonic sort in its all-ascending form, in place in global memory.
-// The sequence is treated as padded to a power of two with +infinity; a compare-exchange
-// whose upper partner lies in the padding never swaps, so it is simply skipped.
-__global__ void __launch_bounds__(256)
-k_cell_sort_big(const KnnGrid *__restrict__ g, const int *__restrict__ bounds,
-                int *__restrict__ sorig, const int *__restrict__ biglist)
+__global__ void __launch_bounds__(kSortWarps * 32)
+k_sort_large_cells(const float *__restrict__ coords, int n_coords, int nv,
+                   const int64_t *__restrict__ direction, const KnnGrid *__restrict__ g,
+                   const int *__restrict__ bounds, const int *__restrict__ biglist,
+                   const int *__restrict__ hugelist, int n_warp_blocks,
+                   int *__restrict__ sorig, float4 *__restrict__ scoords, int *__restrict__ sbin,
+                   uint8_t *__restrict__ sflag)
 {
+    __shared__ int s_keys[kSortWarps][kWarpSortMaxShared];
     if (g->status != 0) return;
-    const int n_big = g->n_big_cells;
-    for (int w = blockIdx.x; w < n_big; w += gridDim.x) {
-        const int cell = biglist[w];
+    if ((int)blockIdx.x < n_warp_blocks) {
+        const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+        const int n_big = g->n_big_cells;
+        for (int w = blockIdx.x * kSortWarps + wib; w < n_big; w += n_warp_blocks * kSortWarps) {
+            const int cell = biglist[w];
+            const int beg = bounds[cell], n = bounds[cell + 1] - beg;
+            warp_sort_segment(sorig + beg, n, s_keys[wib], lane);
+            __syncwarp();
+            for (int t = lane; t < n; t += 32)
+                place_point(beg + t, sorig[beg + t], cell, coords, n_coords, nv, direction, sorig, scoords,
+                            sbin, sflag);
+            __syncwarp();
+        }
+        return;
+    }
+    const int n_huge = g->n_huge_cells;
+    const int n_cta = gridDim.x - n_warp_blocks;
+    for (int w = blockIdx.x - n_warp_blocks; w < n_huge; w += n_cta) {
+        const int cell = hugelist[w];
         const int beg = bounds[cell], n = bounds[cell + 1] - beg;
-        if (n <= kWarpSortMaxShared) continue;   // done by k_cell_sort_warp
         int *seg = sorig + beg;
         int P = 1;
         while (P < n) P <<= 1;
@@ -359,32 +401,18 @@ k_cell_sort_big(const KnnGrid *__restrict__ g, const int *__restrict__ bounds,
                 __syncthreads();
             }
         }
+        for (int t = threadIdx.x; t < n; t += blockDim.x)
+            place_point(beg + t, seg[t], cell, coords, n_coords, nv, direction, sorig, scoords, sbin, sflag);
+        __syncthreads();
     }
 }
 
-// Step 3: everything else in cell order, gathered through the sorted ids.
-__global__ void __launch_bounds__(256)
-k_gather(const float *__restrict__ coords, int n_vert, int n_coords, int nv,
-         const int64_t *__restrict__ direction, const KnnGrid *__restrict__ g,
-         const int *__restrict__ pbin, const int *__restrict__ sorig,
-         float4 *__restrict__ scoords, int *__restrict__ sbin, uint8_t *__restrict__ sflag)
+// One store of the status word to memory the host can read (mapped pinned memory).
+__global__ void k_publish_status(const int32_t *__restrict__ status_dev, volatile int32_t *status_mapped)
 {
-    const int pos = blockIdx.x * blockDim.x + threadIdx.x;
-    if (pos >= n_vert || g->status != 0) return;
-    const int v = sorig[pos];
-    const float *row = coords + (size_t)v * n_coords;
-    for (int q = 0; q < nv; q++) {
-        float4 o;
-        o.x = 4 * q + 0 < n_coords ? __ldg(row + 4 * q + 0) : 0.f;
-        o.y = 4 * q + 1 < n_coords ? __ldg(row + 4 * q + 1) : 0.f;
-        o.z = 4 * q + 2 < n_coords ? __ldg(row + 4 * q + 2) : 0.f;
-        o.w = 4 * q + 3 < n_coords ? __ldg(row + 4 * q + 3) : 0.f;
-        scoords[(size_t)pos * nv + q] = o;
-    }
-    sbin[pos] = pbin[v];
-    if (direction) {
-        const int64_t d = direction[v];
-        sflag[pos] = (d >= 0 && d <= 2) ? (uint8_t)d : (uint8_t)3;
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        *status_mapped = *status_dev;
+        __threadfence_system();
     }
 }
 
@@ -404,6 +432,15 @@ extern "C" int fgc_read_status(const void *workspace_or_params, int32_t *status_
     FGC_RETURN_IF_CUDA(cudaMemcpyAsync(status_host, workspace_or_params, sizeof(int32_t),
                                        cudaMemcpyDeviceToHost, s));
     FGC_RETURN_IF_CUDA(cudaStreamSynchronize(s));
+    return FGC_OK;
+}
+
+extern "C" int fgc_publish_status(const void *workspace_or_params, int32_t *status_mapped,
+                                  fgc_stream_t stream)
+{
+    if (!workspace_or_params || !status_mapped) return FGC_ERR_BAD_ARGUMENT;
+    fgc::k_publish_status<<<1, 32, 0, (cudaStream_t)stream>>>((const int32_t *)workspace_or_params, status_mapped);
+    FGC_CHECK_LAUNCH();
     return FGC_OK;
 }
 
@@ -428,7 +465,10 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
     int *blocksums = (int *)(ws + L.blocksums);
     int *pbin = (int *)(ws + L.pbin);
     int *prank = (int *)(ws + L.prank);
+    int *stmp = (int *)(ws + L.stmp);
     int *sorig = (int *)(ws + L.sorig);
+    int *biglist = (int *)(ws + L.biglist);
+    int *hugelist = (int *)(ws + L.hugelist);
     int *sbin = (int *)(ws + L.sbin);
     uint8_t *sflag = (uint8_t *)(ws + L.sflag);
     float4 *scoords = (float4 *)(ws + L.scoords);
@@ -454,8 +494,7 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
     const int red_blocks = pt_blocks < 148 * 4 ? pt_blocks : 148 * 4;
     k_minmax<<<red_blocks, 256, 0, s>>>(coords, n, n_coords, n_bin_dims, grid);
     FGC_CHECK_LAUNCH();
-    k_grid_setup<<<1, 32, 0, s>>>(grid, (int32_t *)(ws + L.shelltab), row_splits, (int)n_rs, n, n_bin_dims,
-                                  bins_target, bins_cap);
+    k_grid_setup<<<1, 32, 0, s>>>(grid, row_splits, (int)n_rs, n, n_bin_dims, bins_target, bins_cap);
     FGC_CHECK_LAUNCH();
     // The cell count is only known on the device: the scan grids are sized for the
     // largest table k_grid_setup may choose and surplus blocks return at once.
@@ -467,9 +506,7 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
                                           pbin, prank, 0);
     FGC_CHECK_LAUNCH();
     if (adaptive) {
-        k_cell_stat<<<148 * 4, 256, 0, s>>>(counts, grid);
-        FGC_CHECK_LAUNCH();
-        k_grid_refine<<<1, 32, 0, s>>>(grid, n, seen_target);
+        k_cell_stat_refine<<<148 * 4, 256, 0, s>>>(counts, grid, n, seen_target);
         FGC_CHECK_LAUNCH();
         k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid, 1);
         FGC_CHECK_LAUNCH();
@@ -483,16 +520,15 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
     FGC_CHECK_LAUNCH();
     k_scan_apply<<<scan_blocks, 256, 0, s>>>(counts, &grid->total_bins, 1, blocksums);
     FGC_CHECK_LAUNCH();
-    k_fill_ids<<<pt_blocks, 256, 0, s>>>(n, grid, counts, pbin, prank, sorig);
+    k_fill_ids<<<pt_blocks, 256, 0, s>>>(n, grid, counts, pbin, prank, stmp);
     FGC_CHECK_LAUNCH();
-    k_cell_sort<<<148 * 8, 256, 0, s>>>(grid, counts, sorig, (int *)(ws + L.biglist));
+    k_rank_place<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, L.nv, direction_or_null, grid, counts, pbin,
+                                           prank, stmp, sorig, scoords, sbin, sflag, biglist, hugelist);
     FGC_CHECK_LAUNCH();
-    k_cell_sort_warp<<<148 * 8, 128, 0, s>>>(grid, counts, sorig, (const int *)(ws + L.biglist));
-    FGC_CHECK_LAUNCH();
-    k_cell_sort_big<<<148 * 2, 256, 0, s>>>(grid, counts, sorig, (const int *)(ws + L.biglist));
-    FGC_CHECK_LAUNCH();
-    k_gather<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, L.nv, direction_or_null, grid, pbin, sorig,
-                                       scoords, sbin, sflag);
+    const int n_warp_blocks = 148 * 4;
+    k_sort_large_cells<<<n_warp_blocks + 148, kSortWarps * 32, 0, s>>>(
+        coords, n_coords, L.nv, direction_or_null, grid, counts, biglist, hugelist, n_warp_blocks, sorig,
+        scoords, sbin, sflag);
     FGC_CHECK_LAUNCH();
     return FGC_OK;
 }

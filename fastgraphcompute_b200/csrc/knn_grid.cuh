@@ -34,7 +34,9 @@ struct KnnGrid {
     float ext[3];          // extent of the bounding box per grid dimension
     int32_t bins_cap;      // largest cell count per row split the table can hold
     int32_t refined;       // 1 when the density pass replaced the first grid by a finer one
-    int32_t n_big_cells;   // length of the work list of cells sorted by a whole CTA
+    int32_t n_big_cells;   // length of the work list of cells sorted by one warp each
+    int32_t n_huge_cells;  // length of the work list of cells sorted by one CTA each
+    int32_t stat_blocks_done;   // CTAs of the density pass that have added their share
     unsigned long long sum_sq;   // sum over cells of (points in cell)^2, first grid
     // optional debug counters (filled when a search is launched with count_evals):
     // [0] distance evaluations, [1] 32-candidate steps, [2] list insertions,
@@ -80,13 +82,17 @@ __host__ __device__ inline void shell_item_decode(int d, int u, int &o0, int &o1
     }
 }
 
+// Cells of up to kRankMax points are put in order by ranking (every point counts the smaller
+// ids of its cell); larger cells are sorted by a warp, beyond kWarpSortMaxShared by a CTA.
+constexpr int kRankMax = 32;
+
 constexpr size_t kGridHeaderBytes = 256;
 static_assert(sizeof(KnnGrid) <= kGridHeaderBytes, "grid header too large");
 
 
 // Byte offsets of the workspace sections (all 256-byte aligned).
 struct KnnWorkspace {
-    size_t header, shelltab, counts, blocksums, pbin, prank, sorig, sbin, sflag, done, biglist, scoords, total;
+    size_t header, counts, blocksums, pbin, prank, stmp, sorig, sbin, sflag, done, biglist, hugelist, scoords, total;
     int64_t cap_bins;   // capacity of the cell table (entries), host decision
     int nv;             // float4 per point in the sorted coordinate array
 };
@@ -103,16 +109,17 @@ inline KnnWorkspace knn_workspace_layout(int64_t n_vert, int n_coords, int64_t n
     w.nv = (n_coords + 3) / 4;
     size_t off = 0;
     w.header = off; off += kGridHeaderBytes;
-    w.shelltab = off; off = align_up(off + sizeof(int32_t) * kShellTableEntries, 256);
     w.counts = off; off = align_up(off + sizeof(int32_t) * (size_t)(cap + 1), 256);
     w.blocksums = off; off = align_up(off + sizeof(int32_t) * (size_t)((cap + 1) / kScanTile + 2), 256);
     w.pbin = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.prank = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
+    w.stmp = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.sorig = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.sbin = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.sflag = off; off = align_up(off + (size_t)n_vert, 256);
     w.done = off; off = align_up(off + (size_t)n_vert, 256);
-    w.biglist = off; off = align_up(off + sizeof(int32_t) * (size_t)(n_vert / 13 + 1), 256);
+    w.biglist = off; off = align_up(off + sizeof(int32_t) * (size_t)(n_vert / (kRankMax + 1) + 1), 256);
+    w.hugelist = off; off = align_up(off + sizeof(int32_t) * (size_t)(n_vert / (kWarpSortMaxShared + 1) + 1), 256);
     w.scoords = off; off = align_up(off + sizeof(float4) * (size_t)n_vert * w.nv, 256);
     w.total = off;
     return w;

@@ -21,6 +21,7 @@
 // own; they never change which points are nearest, only which of several equidistant
 // points is kept.
 #include "knn_grid.cuh"
+#include "shell_table.cuh"
 #include "knn_tile.cuh"
 
 namespace fgc {
@@ -31,7 +32,6 @@ struct KnnArgs {
     const int *sbin;
     const uint8_t *sflag;   // nullptr: no direction restriction
     const int *bounds;      // cell boundaries, total_bins + 1 entries
-    const int32_t *shelltab;
     const uint8_t *done;    // nullptr, or 1 where the tile kernel already wrote the row
     KnnGrid *grid;
     int64_t *out_idx;
@@ -268,8 +268,8 @@ k_knn(const KnnArgs a)
             for (int d = merged ? 1 : 0;; ++d) {
                 const bool first = merged && d == 1;
                 const int n_items = first ? 1 + shell_items(1) : shell_items(d);
-                const int32_t *tab = first ? a.shelltab
-                                   : (d <= kShellTableMaxD ? a.shelltab + shell_table_offset(d) : nullptr);
+                const int32_t *tab = first ? kShellTableData
+                                   : (d <= kShellTableMaxD ? kShellTableData + shell_table_offset(d) : nullptr);
                 for (int base = 0; base < n_items; base += 32) {
                     const int u = base + lane;
                     bool valid = u < n_items;
@@ -466,7 +466,6 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     a.sbin = (const int *)(ws + L.sbin);
     a.sflag = has_direction ? (const uint8_t *)(ws + L.sflag) : nullptr;
     a.bounds = (const int *)(ws + L.counts);
-    a.shelltab = (const int32_t *)(ws + L.shelltab);
     a.done = use_tiles ? (const uint8_t *)(ws + L.done) : nullptr;
     a.grid = (KnnGrid *)(ws + L.header);
     a.out_idx = out_idx;
@@ -481,7 +480,7 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
         // marks the rows it completed and the pass below searches the remaining queries.
         KnnTileArgs t;
         t.scoords = a.scoords; t.sorig = a.sorig; t.sbin = a.sbin; t.sflag = a.sflag;
-        t.bounds = a.bounds; t.shelltab = a.shelltab; t.grid = a.grid;
+        t.bounds = a.bounds; t.grid = a.grid;
         t.out_idx = out_idx; t.out_dist = out_distsq;
         t.done = (uint8_t *)(ws + L.done);
         t.n_vert = (int)n_vert; t.K = K; t.n_coords = n_coords; t.tf_compat = tf_compat;

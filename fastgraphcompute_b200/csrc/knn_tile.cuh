@@ -49,7 +49,6 @@ struct KnnTileArgs {
     const int *sbin;
     const uint8_t *sflag;
     const int *bounds;
-    const int32_t *shelltab;
     KnnGrid *grid;
     int64_t *out_idx;
     float *out_dist;
@@ -260,7 +259,7 @@ k_knn_tile(const KnnTileArgs a)
             };
             for (int d = 0; d <= kTileMaxShell; ++d) {
                 const int n_items = shell_items(d);
-                const int32_t *tab = a.shelltab + shell_table_offset(d);
+                const int32_t *tab = kShellTableData + shell_table_offset(d);
                 for (int base = 0; base < n_items; base += 32) {
                     // lane-parallel lookup of up to 32 item ranges
                     {

@@ -67,11 +67,14 @@ def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=Fal
         status_host = None
         if check_status:
             # The status word is final once the grid is built (non-finite input and malformed
-            # row_splits are detected by its first two kernels).  Copy it out now, asynchronously,
-            # and look at it after the search has been launched: the host then waits for the
-            # short grid build only, and the GPU never idles while the host checks.
+            # row_splits are detected by its first two kernels).  A one-thread kernel stores it
+            # into pinned host memory now and the host looks at it after the search has been
+            # launched: the host waits for the short grid build only, the GPU never idles while
+            # the host checks, and -- unlike a device-to-host copy -- the store does not queue
+            # behind bulk result copies that other streams have in flight.
             status_host = torch.empty(1, dtype=torch.int32, pin_memory=True)
-            status_host.copy_(ws[:4].view(torch.int32), non_blocking=True)
+            _cabi.check(_cabi.lib.fgc_publish_status(_cabi.ptr(ws), status_host.data_ptr(), stream),
+                        "fgc_publish_status")
             status_ready = torch.cuda.Event()
             status_ready.record()
         if phase_hook is not None:

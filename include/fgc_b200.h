@@ -193,8 +193,8 @@ int fgc_knn_read_counters(const void *workspace, uint64_t *counters_host,
  *   out_status : [1] int32 in device memory, receives the FGC_STATUS_* word of the call.
  * Limits and rules:
  *   - returns FGC_ERR_STATIC_TOO_LARGE when fgc_knn_workspace_bytes(n_vert, n_coords, n_rs, K)
- *     exceeds FGC_STATIC_WORKSPACE_BYTES (that is at about 60 000 points with up to 4
- *     coordinates and about 48 000 with 5 to 8); nothing is launched in that case;
+ *     exceeds FGC_STATIC_WORKSPACE_BYTES (that is at about 40 000 points with up to 4
+ *     coordinates and about 35 000 with 5 to 8); nothing is launched in that case;
  *   - calls no cudaMalloc/cudaFree or other allocating routine;
  *   - the first call on each GPU looks up the device address of the array
  *     (cudaGetSymbolAddress, with that GPU current); make that first call outside any
@@ -224,6 +224,17 @@ const int32_t *fgc_knn_cell_order(const void *workspace, int64_t n_vert, int32_t
  * host and waits for the stream (the only synchronising call of the library).
  */
 int fgc_read_status(const void *workspace_or_params, int32_t *status_host, fgc_stream_t stream);
+
+/*
+ * The same status word without a copy and without waiting: a one-thread kernel on
+ * `stream` stores it to `status_mapped`, which must be page-locked host memory that
+ * the device can address (cudaHostAlloc / cudaHostRegister under unified addressing).
+ * The host reads it after an event recorded behind this call has completed.  Unlike a
+ * device-to-host copy the store does not queue behind bulk copies of other streams, so
+ * a host that pipelines batches can check every batch without stalling the pipeline.
+ * No counterpart in the reference (its checks synchronise the device).
+ */
+int fgc_publish_status(const void *workspace_or_params, int32_t *status_mapped, fgc_stream_t stream);
 
 /*
  * Gradient of the squared distances with respect to the coordinates (backward).
