@@ -149,6 +149,8 @@ class _BinnedKNN(torch.autograd.Function):
         order = cell_order(ws, coords.shape[0], coords.shape[1], row_splits.numel(), K).clone()
         ctx.save_for_backward(idx, coords)
         ctx.mark_non_differentiable(idx, order)
+        # no zero tensors for the gradients of idx and order (an int64 [N, K] fill per backward)
+        ctx.set_materialize_grads(False)
         return idx, dist, order
 
     @staticmethod

@@ -22,6 +22,7 @@ class _GravNetAggregate(torch.autograd.Function):
         fmean, fmax, argmax = torch_ops.gravnet_aggregate_eager(propagate, neighbor_idx, distsq, order)
         ctx.save_for_backward(propagate, neighbor_idx, distsq, argmax)
         ctx.order = order
+        ctx.set_materialize_grads(False)
         return fmean, fmax
 
     @staticmethod
