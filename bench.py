@@ -468,6 +468,47 @@ def run_b200(args):
                    "inputs": "x 410 MB per GPU (larger than L2)", "steps": 5, "warmup": 3}
         del x, m
 
+    # ---- stacked-GravNet model: the reference's own end-to-end benchmark --------------------
+    # (performance/gravnet_perfm.py:100-160: 64 input features, 4 GravNet layers with k = 64,
+    # propagate 32, space 4, hidden 128, 10 outputs; one step = forward, sum(output)*0 backward,
+    # SGD step, on a fresh randn input of n_nodes points in one event; largest size of its sweep)
+    stacked = None
+    if not args.no_gravnet:
+        from fastgraphcompute_b200.gravnet_model import GravNetModel
+        n_nodes = 200000
+        torch.manual_seed(1000 + rank)
+        sm = GravNetModel(64, 32, 4, 64, 128, 10).to(dev)
+        opt = torch.optim.SGD(sm.parameters(), lr=0.01)
+        srs = torch.tensor([0, n_nodes], dtype=torch.int64, device=dev)
+        xs = [torch.randn((n_nodes, 64), device=dev) for _ in range(4)]
+
+        def sstep(i):
+            opt.zero_grad(set_to_none=True)
+            out = sm(xs[i % len(xs)], srs)
+            (torch.sum(out) * 0.0).backward()
+            opt.step()
+            return out
+
+        for i in range(3):
+            sstep(i)
+        barrier()
+        sp = []
+        for i in range(5):
+            flush.zero_()
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            sstep(i)
+            e1.record()
+            sp.append((e0, e1))
+        barrier()
+        s_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in sp)) / 5
+        stacked = {"train_step_ms": s_ms, "n_gpus": world, "n_nodes_per_gpu": n_nodes,
+                   "config": "GravNetModel(in 64, propagate 32, space 4, k 64, hidden 128, out 10, 4 GravNet layers), "
+                             "one event, forward + backward + SGD step as performance/gravnet_perfm.py",
+                   "steps": 5, "warmup": 3}
+        del sm, opt, xs
+
     # ---- CPU baseline beside it (rank 0, single-GPU runs only) -----------------------------
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -516,6 +557,8 @@ def run_b200(args):
             line["cpu_baseline"] = cpu_baseline
         if gravnet:
             line["gravnet"] = gravnet
+        if stacked:
+            line["stacked_gravnet"] = stacked
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -3,7 +3,8 @@
     python oracle/build_ref.py && python tests/golden/make_golden.py
 
 Needs oracle/_ref/binned_knn_ops.so (built from the unmodified reference
-sources).  Writes tests/golden/{knn,binning,gravnet,misc}.npz.  The tests only
+sources).  Writes tests/golden/{knn,binning,gravnet,misc,stacked}.npz
+(`python make_golden.py stacked` writes only the last).  The tests only
 read those files; they never need the reference checkout.
 """
 import os
@@ -46,8 +47,40 @@ def run_knn(c):
     return out
 
 
+STACKED = dict(n=700, row_splits=[0, 300, 700], in_dim=16, prop_dim=8, space_dim=3, k=10, hidden_dim=32,
+               output_dim=5, num_gravnet_layers=2)
+
+
+def make_stacked():
+    """The stacked-GravNet model (performance/gravnet_perfm.py:20-96 of the reference) with the
+    reference's CPU ops inside every GravNet layer: output and gradients of one step."""
+    from fastgraphcompute_b200.gravnet_model import GravNetModel
+    torch.set_num_threads(1)
+    c = STACKED
+    torch.manual_seed(21)
+    m = GravNetModel(c["in_dim"], c["prop_dim"], c["space_dim"], c["k"], c["hidden_dim"], c["output_dim"],
+                     num_gravnet_layers=c["num_gravnet_layers"], the_op=ref_ops.RefGravNetOp)
+    g = torch.Generator().manual_seed(22)
+    x = torch.randn((c["n"], c["in_dim"]), generator=g, requires_grad=True)
+    rs = torch.tensor(c["row_splits"], dtype=torch.int64)
+    out = m(x, rs)
+    (out ** 2).sum().backward()
+    store = {"in/x": x.detach().numpy(), "out/out": out.detach().numpy(), "out/grad_x": x.grad.numpy()}
+    for k, v in c.items():
+        store["in/" + k] = np.asarray(v)
+    for k, v in m.state_dict().items():
+        store["weights/" + k] = v.numpy()
+    for k, p in m.named_parameters():
+        store["grad/" + k] = p.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "stacked.npz"), **store)
+    print("stacked done")
+
+
 def main():
     torch.set_num_threads(1)
+    if "stacked" in sys.argv[1:]:
+        make_stacked()
+        return
     store = {}
     for name, c in cases.knn_cases().items():
         out = run_knn(c)
@@ -123,6 +156,7 @@ def main():
     rep = ref_ops.ref_index_replacer(torch.tensor(tbr), torch.tensor(rpl)).numpy()
     np.savez_compressed(os.path.join(HERE, "misc.npz"), ir_in=tbr, ir_repl=rpl, ir_out=rep)
     print("misc done")
+    make_stacked()
 
 
 if __name__ == "__main__":

@@ -342,6 +342,31 @@ def test_gravnet_module_golden(golden_dir):
             parity.assert_grad_close(p.grad.cpu().numpy(), c["grad"][k], 2e-5, name + " grad " + k, scale=scale)
 
 
+def test_stacked_gravnet_model_golden(golden_dir):
+    """The stacked-GravNet model of the reference's end-to-end benchmark
+    (performance/gravnet_perfm.py:20-96): output and gradients of one training step against
+    the same model run with the reference's CPU ops inside every GravNet layer.  Two GravNet
+    layers deep, so CPU/GPU rounding differences in the dense layers reach the learned
+    coordinates of the second layer: the bar is 1e-4 of the tensor's scale, not 1e-5."""
+    from fastgraphcompute_b200.gravnet_model import GravNetModel
+    c = np.load(os.path.join(golden_dir, "stacked.npz"))
+    g = lambda k: c["in/" + k]  # noqa: E731
+    m = GravNetModel(int(g("in_dim")), int(g("prop_dim")), int(g("space_dim")), int(g("k")),
+                     int(g("hidden_dim")), int(g("output_dim")),
+                     num_gravnet_layers=int(g("num_gravnet_layers"))).to(DEV)
+    m.load_state_dict({k[len("weights/"):]: torch.as_tensor(c[k]) for k in c.files if k.startswith("weights/")})
+    x = cu(g("x")).requires_grad_(True)
+    out = m(x, cu(g("row_splits"), torch.int64))
+    parity.assert_grad_close(out.detach().cpu().numpy(), c["out/out"], 1e-4, "stacked out")
+    (out ** 2).sum().backward()
+    parity.assert_grad_close(x.grad.cpu().numpy(), c["out/grad_x"], 1e-4, "stacked grad_x")
+    for k, p in m.named_parameters():
+        ref = c["grad/" + k]
+        wk = k.replace(".bias", ".weight")
+        scale = float(np.sqrt(np.mean(c["grad/" + wk].astype(np.float64) ** 2)))
+        parity.assert_grad_close(p.grad.cpu().numpy(), ref, 1e-4, "stacked grad " + k, scale=scale)
+
+
 def test_gravnet_shape_sweep():
     """tests/test_gnn_ops.py:87-105 of the reference: shape sweep on 100 points, int32 row splits."""
     rs = torch.tensor([0, 50, 80, 100], dtype=torch.int32, device=DEV)
