@@ -115,6 +115,40 @@ def cell_order(ws, n_vert, n_coords, n_rs, K):
     return ws[off:off + 4 * n_vert].view(torch.int32)
 
 
+# One reverse-neighbour graph per neighbour-index tensor, shared by the deterministic backward
+# passes that scatter through it (GravNet aggregation first, then the kNN distances): the entry
+# keeps the index tensor alive, so its address cannot be reused while the entry exists, and
+# the kNN backward -- the last consumer in a GravNet layer -- drops it.
+_rgraph_cache = {}
+
+
+def clear_reverse_graph_cache():
+    _rgraph_cache.clear()
+
+
+def reverse_graph(idx, keep):
+    """Reverse-neighbour graph workspace of ``idx`` ([N, K] int64, contiguous) and its size in
+    bytes; built by fgc_build_reverse_graph unless the previous caller left one for this very
+    tensor.  ``keep``: leave it for the next caller (at most one graph is kept)."""
+    n_vert, K = idx.shape
+    stream = _cabi.current_stream(idx.device)
+    key = (idx.data_ptr(), idx._version, n_vert, K, idx.device, getattr(stream, "value", stream))
+    hit = _rgraph_cache.pop(key, None)
+    _rgraph_cache.clear()
+    if hit is not None:
+        rg = hit[1]
+    else:
+        rbytes = _cabi.lib.fgc_reverse_graph_bytes(n_vert, K)
+        if not rbytes:
+            return None, 0
+        rg = torch.empty(rbytes, dtype=torch.uint8, device=idx.device)
+        _cabi.check(_cabi.lib.fgc_build_reverse_graph(
+            _cabi.ptr(idx), n_vert, K, _cabi.ptr(rg), rbytes, stream), "fgc_build_reverse_graph")
+    if keep:
+        _rgraph_cache[key] = (idx, rg)
+    return rg, rg.numel()
+
+
 def knn_backward_raw(grad_dist, idx, coords):
     """Launch the backward (atomic or sorted-segment variant) on prepared tensors."""
     n_vert, n_coords = coords.shape
@@ -122,11 +156,8 @@ def knn_backward_raw(grad_dist, idx, coords):
     out = torch.empty_like(coords)
     with torch.cuda.device(coords.device):
         stream = _cabi.current_stream(coords.device)
-        rbytes = _cabi.lib.fgc_reverse_graph_bytes(n_vert, K) if deterministic_backward else 0
+        rg, rbytes = reverse_graph(idx, keep=False) if deterministic_backward else (None, 0)
         if rbytes:
-            rg = torch.empty(rbytes, dtype=torch.uint8, device=coords.device)
-            _cabi.check(_cabi.lib.fgc_build_reverse_graph(
-                _cabi.ptr(idx), n_vert, K, _cabi.ptr(rg), rbytes, stream), "fgc_build_reverse_graph")
             _cabi.check(_cabi.lib.fgc_binned_knn_bwd_sorted(
                 _cabi.ptr(grad_dist), _cabi.ptr(idx), _cabi.ptr(coords), n_vert, K, n_coords,
                 _cabi.ptr(rg), rbytes, _cabi.ptr(out), stream), "fgc_binned_knn_bwd_sorted")

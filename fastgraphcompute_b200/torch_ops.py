@@ -140,13 +140,11 @@ def gravnet_aggregate_backward_eager(prop: Tensor, idx: Tensor, distsq: Tensor, 
     argmax = argmax.contiguous()
     with torch.cuda.device(prop.device):
         stream = _cabi.current_stream(prop.device)
-        rbytes = 0
+        rg, rbytes = None, 0
         if deterministic_gravnet_backward and P <= 128:
-            rbytes = _cabi.lib.fgc_reverse_graph_bytes(n_vert, K)
+            # kept for the kNN backward of the same layer, which scatters through the same indices
+            rg, rbytes = _knn.reverse_graph(idx, keep=_knn.deterministic_backward)
         if rbytes:
-            rg = torch.empty(rbytes, dtype=torch.uint8, device=prop.device)
-            _cabi.check(_cabi.lib.fgc_build_reverse_graph(
-                _cabi.ptr(idx), n_vert, K, _cabi.ptr(rg), rbytes, stream), "fgc_build_reverse_graph")
             _cabi.check(_cabi.lib.fgc_gravnet_aggregate_bwd_sorted(
                 _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(distsq), _cabi.ptr(argmax), _cabi.ptr(g_mean),
                 _cabi.ptr(g_max), n_vert, K, P, _cabi.ptr(rg), rbytes, _cabi.ptr(d_prop), _cabi.ptr(d_dsq),

@@ -367,6 +367,21 @@ def test_stacked_gravnet_model_golden(golden_dir):
         parity.assert_grad_close(p.grad.cpu().numpy(), ref, 1e-4, "stacked grad " + k, scale=scale)
 
 
+def test_gravnet_conv_front_door_matches_row_split_call():
+    """layer(x, batch) of the PyTorch-Geometric style front door == GravNetOp(x, row_splits)."""
+    from fastgraphcompute_b200.torch_geometric_interface import GravNetConv, strict_batch_from_row_splits
+    torch.manual_seed(5)
+    conv = GravNetConv(12, 16, 3, 8, 9).to(DEV)
+    x = torch.randn((500, 12), device=DEV)
+    rs = torch.tensor([0, 120, 120, 333, 500], dtype=torch.int64, device=DEV)
+    batch = strict_batch_from_row_splits(rs)
+    out = conv(x, batch)
+    # the empty event disappears from the batch vector; neighbour search is per event either way
+    ref = conv.op(x, torch.tensor([0, 120, 333, 500], dtype=torch.int64, device=DEV))[0]
+    assert torch.equal(out, ref)
+    assert torch.equal(conv(x[:120]), conv.op(x[:120], torch.tensor([0, 120], device=DEV))[0])
+
+
 def test_gravnet_shape_sweep():
     """tests/test_gnn_ops.py:87-105 of the reference: shape sweep on 100 points, int32 row splits."""
     rs = torch.tensor([0, 50, 80, 100], dtype=torch.int32, device=DEV)
@@ -469,6 +484,9 @@ def test_gravnet_training_step_is_bit_reproducible_with_sorted_segment_backwards
     torch_ops.deterministic_gravnet_backward = True
     try:
         a = step()
+        # the reverse-neighbour graph built for the aggregation backward served the kNN
+        # backward of the same layer and was dropped there
+        assert km._rgraph_cache == {}
         b = step()
     finally:
         km.deterministic_backward = False
