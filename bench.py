@@ -256,9 +256,15 @@ def run_b200(args):
     d_grad = h_grad.to(dev)
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
 
-    def step_resident():
+    fwd_marks = []
+
+    def step_resident(mark=False):
         c = d_coords.detach().requires_grad_(True)
         idx, dsq = fgc.binned_select_knn(K, c, d_rs)
+        if mark:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            fwd_marks.append(e)
         dsq.backward(d_grad)
         return idx, dsq, c.grad
 
@@ -284,7 +290,7 @@ def run_b200(args):
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
-        step_resident()
+        step_resident(mark=True)
         e1.record()
         pairs.append((e0, e1))
     knn_mod.phase_hook = None
@@ -297,6 +303,10 @@ def run_b200(args):
     ends = [e for t, e in search_events if t == "search_end"]
     knn_ms = [a.elapsed_time(b) for a, b in zip(begins, ends)]
     knn_ms_avg = sum(knn_ms) / len(knn_ms)
+    phases = {"fwd_ms_median": statistics.median(a.elapsed_time(m_) for (a, _), m_ in zip(pairs, fwd_marks)),
+              "bwd_ms_median": statistics.median(m_.elapsed_time(b) for (_, b), m_ in zip(pairs, fwd_marks)),
+              "fwd_bwd_ms_median": statistics.median(step_ms),
+              "search_kernel_ms_median": statistics.median(knn_ms)}
 
     # ---- end to end from host buffers ("e2e") --------------------------------------------------
     o_idx = torch.empty((n, K), dtype=torch.int64).pin_memory()
@@ -509,6 +519,49 @@ def run_b200(args):
                    "steps": 5, "warmup": 3}
         del sm, opt, xs
 
+    # ---- event-batched workload C3 sharded by event over the ranks (strong scaling) ----------
+    # Every rank holds the batch, searches the events the partition table gives it (no
+    # collective) and, with more than one rank, gathers the rows of all ranks (the one
+    # exchange step of the multi-GPU path).
+    c3 = None
+    if not args.no_gravnet:
+        from fastgraphcompute_b200 import event_sharding
+        w3 = synthetic.c3_event_batch(seed=0)
+        part = event_sharding.partition_events(w3.row_splits, world)
+        c3_coords = w3.coords.to(dev)
+
+        def c3_search():
+            return event_sharding.local_binned_select_knn(w3.K, c3_coords, w3.row_splits, part.events[rank])
+
+        for _ in range(2):
+            res = c3_search()
+        del res
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e2 = torch.cuda.Event(enable_timing=True)
+        c3_reps = 3
+        e0.record()
+        for _ in range(c3_reps):
+            rows, idx3, dsq3 = c3_search()
+        e1.record()
+        if world > 1:
+            full = event_sharding.gather_rows(rows, [idx3, dsq3], w3.n_points, part.points)
+            del full
+        e2.record()
+        barrier()
+        c3_ms = max_over_ranks(e0.elapsed_time(e1)) / c3_reps
+        c3_gather_ms = max_over_ranks(e1.elapsed_time(e2)) if world > 1 else 0.0
+        c3 = {"config": "c3: 64 events of 50000..150000 uniform points, D=3, K=64, forward, sharded by event "
+                        "(greedy longest-processing-time on point counts)",
+              "n_points": w3.n_points, "n_gpus": world, "search_ms": c3_ms,
+              "points_per_s": w3.n_points / (c3_ms * 1e-3),
+              "gather_ms": c3_gather_ms, "scaling": "strong",
+              "largest_shard_points": max(part.points),
+              "note": "search_ms: local search + local->global ids, max over ranks; gather_ms: padded "
+                      "all_gather of idx and distsq to every rank (NCCL), once"}
+        del rows, idx3, dsq3, c3_coords
+
     # ---- CPU baseline beside it (rank 0, single-GPU runs only) -----------------------------
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -559,6 +612,9 @@ def run_b200(args):
             line["gravnet"] = gravnet
         if stacked:
             line["stacked_gravnet"] = stacked
+        if c3:
+            line["c3_event_sharded"] = c3
+        line["phases"] = phases
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
