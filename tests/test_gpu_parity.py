@@ -142,6 +142,62 @@ def test_knn_golden(golden_dir):
     assert ties < 50
 
 
+def _random_knn_case(seed):
+    """One small random problem: sizes, dimensions, K, event layout (with empty and tiny events),
+    point distribution (uniform, clustered, coarse lattice with exact ties, exact duplicates),
+    direction flags and the tf_compat switch all drawn from the seed."""
+    rng = np.random.RandomState(seed)
+    n_events = int(rng.randint(1, 6))
+    sizes = [int(rng.choice([0, 1, 2, rng.randint(3, 40), rng.randint(40, 1200)])) for _ in range(n_events)]
+    if sum(sizes) == 0:
+        sizes[0] = 5
+    n = sum(sizes)
+    d = int(rng.randint(2, 7))
+    k = int(rng.choice([1, 2, 5, 16, 32, 33, 40, 70]))
+    kind = rng.randint(0, 4)
+    if kind == 0:
+        coords = rng.rand(n, d)
+    elif kind == 1:
+        centres = rng.rand(6, d)
+        coords = centres[rng.randint(0, 6, n)] + 0.01 * rng.randn(n, d)
+    elif kind == 2:
+        coords = rng.randint(0, 5, (n, d)) * 0.25
+    else:
+        coords = rng.rand(n, d)
+        half = n // 2
+        coords[half:2 * half] = coords[:half]
+    coords = (coords * float(rng.choice([1e-3, 1.0, 50.0])) + float(rng.choice([0.0, -3.0, 100.0]))).astype(np.float32)
+    rs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    direction = rng.randint(0, 4, n).astype(np.int64) if rng.rand() < 0.3 else None
+    return dict(coords=coords, row_splits=rs, K=k, direction=direction, tf_compat=bool(rng.rand() < 0.25),
+                grad=rng.randn(n, k).astype(np.float32))
+
+
+def test_knn_random_configurations_vs_oracle():
+    """60 seeded random problems through the public call against the CPU oracle: rows as sets
+    (1-ulp ties allowed at the K-th distance only), distances, and the gradient."""
+    worst = 0.0
+    for seed in range(60):
+        c = _random_knn_case(seed)
+        what = "random case %d (N=%d D=%d K=%d)" % (seed, c["coords"].shape[0], c["coords"].shape[1], c["K"])
+        coords = cu(c["coords"]).requires_grad_(True)
+        dirn = None if c["direction"] is None else cu(c["direction"])
+        idx, dist = fgc.binned_select_knn(c["K"], coords, cu(c["row_splits"]), direction=dirn,
+                                          torch_compatible_indices=c["tf_compat"])
+        oi, od = oracle.binned_select_knn(c["K"], c["coords"], c["row_splits"], direction=c["direction"],
+                                          torch_compatible_indices=c["tf_compat"])
+        st = parity.assert_knn_parity(idx.cpu().numpy(), dist.detach().cpu().numpy(), oi, od,
+                                      pad_self=c["tf_compat"], what=what)
+        worst = max(worst, st["max_rel"])
+        # gradient on the library's own rows (the oracle's backward takes any index rows)
+        (dist * cu(c["grad"])).sum().backward()
+        plain = np.where(idx.cpu().numpy() == np.arange(idx.shape[0])[:, None], -1, idx.cpu().numpy()) \
+            if c["tf_compat"] else idx.cpu().numpy()
+        og = oracle.binned_select_knn_grad(c["grad"], plain, c["coords"])
+        parity.assert_grad_close(coords.grad.cpu().numpy(), og, what=what + " grad")
+    assert worst <= parity.DIST_RTOL
+
+
 def test_knn_gradient_on_reference_slot_order(golden_dir):
     """The backward entry point alone, fed the reference's own index rows."""
     from fastgraphcompute_b200 import _cabi
