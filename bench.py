@@ -597,6 +597,18 @@ def run_b200(args):
                         "sample": "the full workload once (200000 points, fwd+bwd, %.1f s)" % t,
                         "aten_threads": torch.get_num_threads(),
                         "note": "the reference's kNN, binning and gradient loops are single-threaded"}
+        # distance evaluations of the reference's own shell walk at its default binning, counted
+        # by the instrumented C restatement on the same workload (beside the count of this search)
+        try:
+            from oracle import oracle as _oracle
+            t0 = time.time()
+            _, _, c_ref = _oracle.binned_select_knn(wb.K, wb.coords.numpy(), wb.row_splits.numpy(), return_evals=True)
+            cpu_baseline["reference_binning_evals_per_query"] = c_ref / wb.n_points
+            cpu_baseline["reference_binning_evals_note"] = (
+                "C restatement of the reference forward with its default n_bins, %.1f s" % (time.time() - t0))
+        except Exception as exc:      # noqa: BLE001
+            cpu_baseline["reference_binning_evals_per_query"] = None
+            cpu_baseline["reference_binning_evals_note"] = "not counted: %r" % (exc,)
 
     if rank == 0:
         peak, peak_kind = measured_peaks()
