@@ -71,15 +71,25 @@ def partition_events(row_splits, world_size: int, weights: Optional[Sequence[flo
 
 
 def shard_rows(row_splits, events: Sequence[int], device=None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Global row ids (int64, concatenated event by event) and local row splits of a shard."""
-    rs = torch.as_tensor(row_splits).cpu().to(torch.int64)
-    pieces = [torch.arange(int(rs[e]), int(rs[e + 1]), dtype=torch.int64) for e in events]
-    rows = torch.cat(pieces) if pieces else torch.zeros(0, dtype=torch.int64)
+    """Global row ids (int64, concatenated event by event) and local row splits of a shard.
+
+    Only the per-event starts and sizes (a few numbers) are prepared on the host; the row ids
+    themselves are generated on ``device``:  row = position in the shard + (start of its event
+    in the batch - start of its event in the shard)."""
+    rs = [int(v) for v in torch.as_tensor(row_splits).cpu().tolist()]
+    starts = [rs[e] for e in events]
+    sizes = [rs[e + 1] - rs[e] for e in events]
+    n_local = sum(sizes)
     local = torch.zeros(len(events) + 1, dtype=torch.int64)
     if events:
-        local[1:] = torch.cumsum(torch.tensor([int(rs[e + 1] - rs[e]) for e in events]), 0)
-    if device is not None:
-        rows, local = rows.to(device), local.to(device)
+        local[1:] = torch.cumsum(torch.tensor(sizes, dtype=torch.int64), 0)
+    dev = device if device is not None else torch.device("cpu")
+    local = local.to(dev)
+    if n_local == 0:
+        return torch.zeros(0, dtype=torch.int64, device=dev), local
+    shift = torch.tensor(starts, dtype=torch.int64, device=dev) - local[:-1]
+    rows = torch.arange(n_local, dtype=torch.int64, device=dev) + torch.repeat_interleave(
+        shift, torch.tensor(sizes, dtype=torch.int64, device=dev), output_size=n_local)
     return rows, local
 
 
