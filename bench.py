@@ -572,6 +572,9 @@ def run_b200(args):
                 barrier()
                 g0 = torch.cuda.Event(enable_timing=True)
                 g1 = torch.cuda.Event(enable_timing=True)
+                full = event_sharding.gather_rows(rows, [idx3, dsq3], w3.n_points, part.points)   # warm-up
+                del full
+                barrier()
                 g0.record()
                 full = event_sharding.gather_rows(rows, [idx3, dsq3], w3.n_points, part.points)
                 g1.record()
@@ -585,7 +588,7 @@ def run_b200(args):
                   "gather_ms": c3_gather_ms, "scaling": "strong",
                   "largest_shard_points": max(part.points),
                   "note": "search_ms: local search + local->global ids, max over ranks; gather_ms: padded "
-                          "all_gather of idx and distsq to every rank (NCCL), once"}
+                          "all_gather of idx and distsq to every rank (NCCL), second call"}
         rows = idx3 = dsq3 = c3_coords = None
 
     # ---- CPU baseline beside it (rank 0, single-GPU runs only) -----------------------------

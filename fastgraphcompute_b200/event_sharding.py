@@ -151,16 +151,18 @@ def gather_rows(rows, tensors, n_total, points_per_rank, group=None):
         p[: t.shape[0]] = t
         return p
 
-    rows_all = [torch.empty((n_max,), dtype=rows.dtype, device=rows.device) for _ in range(world)]
-    dist.all_gather(rows_all, pad(rows), group=group)
+    # one receive buffer per tensor ([world * n_max, ...], rank r's block at r * n_max): a single
+    # collective each, no per-rank staging copies
+    rows_all = torch.empty((world * n_max,), dtype=rows.dtype, device=rows.device)
+    dist.all_gather_into_tensor(rows_all, pad(rows), group=group)
     outs = []
     for t in tensors:
-        parts = [torch.empty((n_max,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
-                 for _ in range(world)]
-        dist.all_gather(parts, pad(t), group=group)
+        buf = torch.empty((world * n_max,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(buf, pad(t), group=group)
         full = torch.empty((n_total,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
         for r in range(world):
-            full.index_copy_(0, rows_all[r][: all_sizes[r]], parts[r][: all_sizes[r]])
+            lo = r * n_max
+            full.index_copy_(0, rows_all[lo: lo + all_sizes[r]], buf[lo: lo + all_sizes[r]])
         outs.append(full)
     return outs
 
