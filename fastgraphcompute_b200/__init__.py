@@ -11,7 +11,8 @@ from . import torch_ops  # noqa: F401  (registers the fgc_b200 dispatcher ops)
 from .extensions.bin_by_coordinates import bin_by_coordinates
 from .extensions.binned_select_knn import binned_select_knn
 from .extensions.index_replacer import index_replacer
-from .extensions.oc_helper import select_with_default
+from .extensions.oc_helper import oc_helper_matrices, select_with_default
 
 __version__ = "0.1.0"
-__all__ = ["bin_by_coordinates", "binned_select_knn", "index_replacer", "select_with_default"]
+__all__ = ["bin_by_coordinates", "binned_select_knn", "index_replacer", "select_with_default",
+           "oc_helper_matrices"]

@@ -37,6 +37,7 @@ KERNELS_KNN_BWD = 1
 KERNELS_KNN_BWD_SORTED = 7   # reverse graph (6) + gather (1)
 KERNELS_GRAVNET_FWD = 1
 KERNELS_GRAVNET_BWD = 1
+KERNELS_OC_PREPARE = 8          # + the radix sort's own kernels
 
 STATUS_NONFINITE = 1
 STATUS_BAD_ROW_SPLITS = 2
@@ -107,6 +108,13 @@ SIGNATURES = {
                                                         c_void_p, c_i64, c_i32, c_i32, c_void_p, c_size,
                                                         c_void_p, c_void_p, c_void_p, c_void_p]),
     "fgc_knn_cell_order": (c_void_p, [c_void_p, c_i64, c_i32, c_i64, c_i32]),
+    "fgc_oc_workspace_bytes": (c_size, [c_i64]),
+    "fgc_oc_prepare": (ctypes.c_int, [c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_size, c_void_p, c_void_p]),
+    "fgc_oc_read_sizes": (ctypes.c_int, [c_void_p, ctypes.POINTER(c_i32), ctypes.POINTER(c_i64), c_void_p]),
+    "fgc_oc_fill": (ctypes.c_int, [c_void_p, c_size, c_i64, c_void_p, c_i64, c_i64, c_i64, c_void_p, c_void_p,
+                                   c_void_p]),
+    "fgc_select_with_default": (ctypes.c_int, [c_void_p, c_i64, c_void_p, c_i64, c_i64, c_i32, c_void_p,
+                                               c_void_p, c_void_p]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

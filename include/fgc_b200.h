@@ -320,6 +320,45 @@ int fgc_gravnet_aggregate_bwd_sorted(const float *prop, const int64_t *idx, cons
                                      float *out_d_distsq, const int32_t *order_or_null,
                                      fgc_stream_t stream);
 
+/*
+ * Object-condensation index matrices -- the consumers of the same row_splits data on the loss
+ * side (the reference's oc_helper_matrices: extensions/oc_helper.py:128-230 ->
+ * oc_helper_cpu.cpp:117-156 / oc_helper_cuda_kernel.cu, helper oc_helper_helper.cpp:31-93).
+ *
+ * An object is the set of points of ONE row split that share a non-negative truth index.
+ *   M[n_unique, n_maxuq]     point ids of each object, ascending, padded with -1
+ *   M_not[n_unique, n_maxrs] ids of all other points of the object's row split, ascending, -1 padded
+ *   objects_per_split[n_rs-1]
+ * n_unique, n_maxuq (largest object) and n_maxrs (largest row split) are only known on the
+ * device, so the work is split like the reference's (which computes them on the host first):
+ *   fgc_oc_prepare     sorts (truth index, point id), finds the objects, writes objects_per_split
+ *   fgc_oc_read_sizes  status word + {n_unique, n_maxuq, n_maxrs}; waits for the stream
+ *   fgc_oc_fill        writes M and, when out_M_not_or_null != NULL, M_not
+ * The rows are ordered by (truth index, row split); the reference leaves the order open.
+ * asso_idx[n_vert] int64, row_splits[n_rs] int64 (validated: status FGC_STATUS_BAD_ROW_SPLITS).
+ */
+size_t fgc_oc_workspace_bytes(int64_t n_vert);
+int fgc_oc_prepare(const int64_t *asso_idx, int64_t n_vert, const int64_t *row_splits, int64_t n_rs,
+                   void *workspace, size_t workspace_bytes, int64_t *objects_per_split,
+                   fgc_stream_t stream);
+int fgc_oc_read_sizes(const void *workspace, int32_t *status_host, int64_t sizes_host[3],
+                      fgc_stream_t stream);
+int fgc_oc_fill(const void *workspace, size_t workspace_bytes, int64_t n_vert, const int64_t *row_splits,
+                int64_t n_unique, int64_t n_maxuq, int64_t n_maxrs, int64_t *out_M,
+                int64_t *out_M_not_or_null, fgc_stream_t stream);
+
+/*
+ * out[e, :] = feat[idx[e], :] for idx[e] in [0, n_rows_feat), else the default value
+ * (the reference's select_with_default, extensions/oc_helper.py:232-271, which builds the
+ * result from a full(), a nonzero() and two advanced-index passes).  idx[n_idx] int64 (the
+ * flattened [V, K] index matrix), feat[n_rows_feat, n_feat] of 4- or 8-byte elements
+ * (word_bytes), default_word_host: the default value's bit pattern, read on the host at
+ * call time; out[n_idx, n_feat] of the same element type.
+ */
+int fgc_select_with_default(const int64_t *idx, int64_t n_idx, const void *feat, int64_t n_rows_feat,
+                            int64_t n_feat, int32_t word_bytes, const void *default_word_host,
+                            void *out, fgc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -24,6 +24,8 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT_SO = os.path.join(OUT_DIR, "binned_knn_ops.so")
+# single-file op libraries of the loss-side helpers (setup.py:139-159 of the reference)
+EXTRA_LIBS = {"oc_helper_cpu.so": ["oc_helper_cpu.cpp"], "oc_helper_helper.so": ["oc_helper_helper.cpp"]}
 
 CPU_SOURCES = [
     "binned_knn_autograd_kernel.cpp",
@@ -50,8 +52,12 @@ def build(reference_root=None, force=False, verbose=True):
         return None
     srcs = [os.path.join(ext_dir, s) for s in CPU_SOURCES]
     srcs.append(os.path.join(HERE, "ref_cuda_stubs.cpp"))
-    if (not force and os.path.exists(OUT_SO)
-            and all(os.path.getmtime(OUT_SO) >= os.path.getmtime(s) for s in srcs)):
+    targets = {OUT_SO: srcs}
+    for name, files in EXTRA_LIBS.items():
+        targets[os.path.join(OUT_DIR, name)] = [os.path.join(ext_dir, f) for f in files]
+    stale = {so: ss for so, ss in targets.items()
+             if force or not os.path.exists(so) or any(os.path.getmtime(so) < os.path.getmtime(x) for x in ss)}
+    if not stale:
         return OUT_SO
 
     import torch
@@ -77,16 +83,18 @@ def build(reference_root=None, force=False, verbose=True):
             raise RuntimeError("compile failed: %s\n%s" % (" ".join(cmd), r.stderr[-4000:]))
         return obj
 
-    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
-        objs = list(ex.map(compile_one, srcs))
     lib_dir = os.path.join(os.path.dirname(torch.__file__), "lib")
-    link = ["g++", "-shared", "-o", OUT_SO] + objs + [
-        "-L", lib_dir, "-Wl,-rpath," + lib_dir, "-ltorch", "-ltorch_cpu", "-lc10"]
-    r = subprocess.run(link, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError("link failed:\n" + r.stderr[-4000:])
-    if verbose:
-        print("built", OUT_SO)
+    all_srcs = sorted({x for ss in stale.values() for x in ss})
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
+        obj_of = dict(zip(all_srcs, ex.map(compile_one, all_srcs)))
+    for so, ss in stale.items():
+        link = ["g++", "-shared", "-o", so] + [obj_of[x] for x in ss] + [
+            "-L", lib_dir, "-Wl,-rpath," + lib_dir, "-ltorch", "-ltorch_cpu", "-lc10"]
+        r = subprocess.run(link, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("link failed:\n" + r.stderr[-4000:])
+        if verbose:
+            print("built", so)
     return OUT_SO
 
 

@@ -151,6 +151,43 @@ def select_with_default(idx, feat, default_value):
     return out
 
 
+def oc_helper_matrices(truth_idxs, row_splits, calc_m_not=True):
+    """Oracle for oc_helper_matrices (extensions/oc_helper.py:128-230): the unique
+    (truth index, row split) pairs with a non-negative index (oc_helper.py:100-118), the two
+    scalar sizes (oc_helper_helper.cpp:31-93) and the per-object scans of calc_m
+    (oc_helper_cpu.cpp:14-83).  Objects are listed by (row split, truth index) -- what a stable
+    argsort gives at oc_helper.py:187; the reference's own order there is unspecified, so
+    callers compare the rows as a set keyed by their first entry.
+
+    Returns (M [K, n_maxuq], M_not [K, n_maxrs], objects_per_split [R])."""
+    asso = np.asarray(truth_idxs, np.int64).reshape(-1)
+    rs = np.asarray(row_splits, np.int64)
+    n_splits = len(rs) - 1
+    objects = []
+    per_split = np.zeros(n_splits, np.int64)
+    n_maxuq = 0
+    for e in range(n_splits):
+        part = asso[rs[e]:rs[e + 1]]
+        vals = np.unique(part[part >= 0])
+        per_split[e] = len(vals)
+        for v in vals:
+            objects.append((e, int(v)))
+            n_maxuq = max(n_maxuq, int((part == v).sum()))
+    n_maxrs = int((rs[1:] - rs[:-1]).max()) if n_splits > 0 else 0
+    M = np.full((len(objects), n_maxuq), -1, np.int64)
+    M_not = np.full((len(objects), n_maxrs), -1, np.int64)
+    for k, (e, v) in enumerate(objects):
+        fill = fill_not = 0
+        for i_v in range(int(rs[e]), int(rs[e + 1])):
+            if asso[i_v] == v:
+                M[k, fill] = i_v
+                fill += 1
+            elif calc_m_not:
+                M_not[k, fill_not] = i_v
+                fill_not += 1
+    return M, M_not, per_split
+
+
 def gravnet_aggregate_fwd(prop, idx, distsq):
     """Oracle for steps 4-7 of GravNetOp.forward (gnn_ops.py:90-102)."""
     L = _lib()

@@ -141,3 +141,46 @@ class RefGravNetOp(torch.nn.Module):
         fmean, fmax = ref_gravnet_aggregate(propagate, idx, distsq)
         out = self.output_transformations(torch.cat([x, fmean, fmax], dim=1))
         return out, idx, distsq, space
+
+
+# --------------------------------------------------------------------------- oc_helper
+
+_OC_SOS = [os.path.join(_HERE, "_ref", "oc_helper_cpu.so"), os.path.join(_HERE, "_ref", "oc_helper_helper.so")]
+_oc_loaded = False
+
+
+def oc_available():
+    return all(os.path.exists(p) for p in _OC_SOS)
+
+
+def ref_oc_helper_matrices(truth_idxs, row_splits, calc_m_not=True):
+    """Reference oc_helper_matrices on CPU tensors: the orchestration of
+    extensions/oc_helper.py:100-230 restated around the reference's own ops
+    oc_helper_helper::max_same_valued_entries_per_row_split (oc_helper_helper.cpp:31-93) and
+    oc_helper_cpu::oc_helper_cpu (oc_helper_cpu.cpp:117-156).  The argsort that orders the
+    objects by row split is made stable here (the reference's is not, so its order among the
+    objects of one row split is unspecified)."""
+    global _oc_loaded
+    if not _oc_loaded:
+        if not oc_available():
+            raise RuntimeError("oracle/_ref/oc_helper_*.so missing: run python oracle/build_ref.py")
+        for p in _OC_SOS:
+            torch.ops.load_library(p)
+        _oc_loaded = True
+    truth_idxs = truth_idxs.to(torch.int64)
+    row_splits = row_splits.to(torch.int64)
+    lengths = row_splits[1:] - row_splits[:-1]
+    max_length = torch.max(lengths)
+    row_ids = torch.repeat_interleave(torch.arange(len(lengths), dtype=torch.int64), lengths)
+    pairs = torch.stack((truth_idxs, row_ids), dim=1)
+    pairs = torch.unique(pairs[pairs[:, 0] != -1], dim=0)
+    pairs = pairs[pairs[:, 0] >= 0]
+    _, max_same, per_split = torch.ops.oc_helper_helper.max_same_valued_entries_per_row_split(
+        truth_idxs, row_splits, True)
+    order = torch.argsort(pairs[:, 1], stable=True)
+    unique_idxs = pairs[order, 0].contiguous()
+    unique_rs = pairs[order, 1].contiguous()
+    M, M_not = torch.ops.oc_helper_cpu.oc_helper_cpu(
+        truth_idxs.contiguous(), unique_idxs, unique_rs, row_splits.contiguous(),
+        max_same.to(torch.int64).reshape(1), max_length.reshape(1), bool(calc_m_not))
+    return M, M_not, per_split

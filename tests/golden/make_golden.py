@@ -3,8 +3,8 @@
     python oracle/build_ref.py && python tests/golden/make_golden.py
 
 Needs oracle/_ref/binned_knn_ops.so (built from the unmodified reference
-sources).  Writes tests/golden/{knn,binning,gravnet,misc,stacked}.npz
-(`python make_golden.py stacked` writes only the last).  The tests only
+sources).  Writes tests/golden/{knn,binning,gravnet,misc,stacked,oc}.npz
+(`python make_golden.py stacked` / `oc` write only that file).  The tests only
 read those files; they never need the reference checkout.
 """
 import os
@@ -76,10 +76,49 @@ def make_stacked():
     print("stacked done")
 
 
+def oc_cases():
+    rng = np.random.RandomState(77)
+    cases = {}
+
+    def mk(name, sizes, lo, hi, scale=1):
+        rs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+        asso = rng.randint(lo, hi, size=int(rs[-1])).astype(np.int64)
+        asso[asso >= 0] *= scale
+        cases[name] = dict(asso=asso, row_splits=rs)
+
+    mk("two_splits", [40, 25], -2, 6)
+    mk("empty_split_between", [30, 0, 50], -1, 9)
+    mk("large_truth_indices", [60, 60, 10], -3, 12, scale=10 ** 12 + 7)
+    mk("many_small_objects", [300], 0, 150)
+    mk("one_object_per_split", [20, 20, 20], 5, 6)
+    mk("noise_only_split", [25, 40], -4, 0)
+    cases["noise_only_split"]["asso"][25:] = rng.randint(0, 4, size=40)
+    mk("bigger", [700, 900, 400], -1, 40)
+    return cases
+
+
+def make_oc():
+    """oc_helper_matrices of the reference (its CPU ops, extensions/oc_helper_cpu.cpp and
+    oc_helper_helper.cpp) on small seeded cases."""
+    store = {}
+    for name, c in oc_cases().items():
+        M, M_not, per = ref_ops.ref_oc_helper_matrices(torch.tensor(c["asso"]), torch.tensor(c["row_splits"]))
+        store[name + "/in/asso"] = c["asso"]
+        store[name + "/in/row_splits"] = c["row_splits"]
+        store[name + "/out/M"] = M.numpy()
+        store[name + "/out/M_not"] = M_not.numpy().astype(np.int32)
+        store[name + "/out/per_split"] = per.numpy()
+    np.savez_compressed(os.path.join(HERE, "oc.npz"), **store)
+    print("oc done")
+
+
 def main():
     torch.set_num_threads(1)
     if "stacked" in sys.argv[1:]:
         make_stacked()
+        return
+    if "oc" in sys.argv[1:]:
+        make_oc()
         return
     store = {}
     for name, c in cases.knn_cases().items():
@@ -157,6 +196,7 @@ def main():
     np.savez_compressed(os.path.join(HERE, "misc.npz"), ir_in=tbr, ir_repl=rpl, ir_out=rep)
     print("misc done")
     make_stacked()
+    make_oc()
 
 
 if __name__ == "__main__":

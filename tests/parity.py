@@ -118,3 +118,26 @@ def brute_force_knn(coords, row_splits, K):
         dd[:, 0] = 0
         dist[lo:hi, :m] = dd
     return idx, dist
+
+
+def canonical_object_rows(M, M_not):
+    """Rows of (M, M_not) ordered by the first point of every object.  The order of the objects
+    is left open by the reference (oc_helper.py:91-92, its own test sorts too:
+    tests/test_oc_helper.py:10-26); the first member id identifies an object uniquely."""
+    M = np.asarray(M, np.int64)
+    M_not = np.asarray(M_not, np.int64)
+    if M.shape[0] == 0:
+        return M, M_not
+    order = np.argsort(M[:, 0], kind="stable")
+    return M[order], M_not[order]
+
+
+def assert_oc_matrices_equal(M, M_not, per_split, ref_M, ref_M_not, ref_per_split, what=""):
+    """Bit-exact equality of the index matrices up to the order of the objects."""
+    assert np.array_equal(np.asarray(per_split, np.int64), np.asarray(ref_per_split, np.int64)), what + " objects per split"
+    assert tuple(np.shape(M)) == tuple(np.shape(ref_M)), what + " M shape %s vs %s" % (np.shape(M), np.shape(ref_M))
+    assert tuple(np.shape(M_not)) == tuple(np.shape(ref_M_not)), what + " M_not shape"
+    a, an = canonical_object_rows(M, M_not)
+    b, bn = canonical_object_rows(ref_M, ref_M_not)
+    assert np.array_equal(a, b), what + " M differs"
+    assert np.array_equal(an, bn), what + " M_not differs"

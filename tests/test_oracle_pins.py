@@ -200,3 +200,56 @@ def test_gravnet_backward_oracle_matches_autograd():
                                           gm.numpy(), gx.numpy())
     parity.assert_grad_close(dp, prop.grad.numpy(), 1e-5, "d_prop")
     parity.assert_grad_close(dd, dsq.grad.numpy(), 1e-5, "d_distsq")
+
+
+# ---- oc_helper_matrices --------------------------------------------------------------------
+
+OC_KNOWN_ASSO = [3, 7, 3, -1, -1, 3, 7, 1, 1, 0, 0, -1, 1, 1, -1, 3, -1, 19, 3, 2, -1, 19]
+OC_KNOWN_RS = [0, 15, 22]
+OC_KNOWN_M = [[0, 2, 5, -1], [1, 6, -1, -1], [7, 8, 12, 13], [9, 10, -1, -1],
+              [15, 18, -1, -1], [17, 21, -1, -1], [19, -1, -1, -1]]
+
+
+def oc_known_m_not():
+    """M_not of the reference's known-answer case (tests/test_oc_helper.py:88-112): every point
+    of the object's row split that is not in the object, ascending, padded to 15."""
+    rows = []
+    for members in OC_KNOWN_M:
+        first = members[0]
+        lo, hi = (0, 15) if first < 15 else (15, 22)
+        others = [i for i in range(lo, hi) if i not in members]
+        rows.append(others + [-1] * (15 - len(others)))
+    return rows
+
+
+def test_oc_helper_known_answer():
+    """tests/test_oc_helper.py:28-125 of the reference."""
+    M, M_not, per = oracle.oc_helper_matrices(OC_KNOWN_ASSO, OC_KNOWN_RS)
+    assert M.shape == (7, 4) and M_not.shape == (7, 15)
+    parity.assert_oc_matrices_equal(M, M_not, per, OC_KNOWN_M, oc_known_m_not(), [4, 3], "known answer")
+
+
+def test_oc_helper_golden(golden_dir):
+    for name, c in load(golden_dir, "oc").items():
+        M, M_not, per = oracle.oc_helper_matrices(c["in"]["asso"], c["in"]["row_splits"])
+        parity.assert_oc_matrices_equal(M, M_not, per, c["out"]["M"], c["out"]["M_not"], c["out"]["per_split"], name)
+        M2, M_not2, _ = oracle.oc_helper_matrices(c["in"]["asso"], c["in"]["row_splits"], calc_m_not=False)
+        assert np.array_equal(M2, M) and (M_not2 == -1).all()
+
+
+def test_oc_helper_live_reference():
+    from oracle import ref_ops
+    if not ref_ops.oc_available():
+        pytest.skip("oracle/_ref/oc_helper_*.so not built (needs the reference checkout)")
+    import torch
+    rng = np.random.RandomState(5)
+    for trial in range(10):
+        sizes = [int(rng.randint(0, 80)) for _ in range(rng.randint(1, 5))]
+        if sum(sizes) == 0:
+            sizes[0] = 4
+        rs = np.concatenate([[0], np.cumsum(sizes)])
+        asso = rng.randint(-2, 9, size=int(rs[-1])).astype(np.int64)
+        M, M_not, per = oracle.oc_helper_matrices(asso, rs)
+        rM, rM_not, rper = ref_ops.ref_oc_helper_matrices(torch.tensor(asso), torch.tensor(rs))
+        assert np.array_equal(M, rM.numpy()) and np.array_equal(M_not, rM_not.numpy())
+        assert np.array_equal(per, rper.numpy())
