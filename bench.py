@@ -591,6 +591,74 @@ def run_b200(args):
                           "all_gather of idx and distsq to every rank (NCCL), second call"}
         rows = idx3 = dsq3 = c3_coords = None
 
+    # ---- object-condensation index matrices (the loss-side consumer of the same row splits) --
+    oc = None
+    if not args.no_gravnet:
+        oc_local = None
+        try:
+            import ctypes
+            g_oc = torch.Generator().manual_seed(3 + rank)
+            n_sp, per_sp = 16, 100000
+            asso = torch.randint(-20, 200, (n_sp * per_sp,), generator=g_oc).to(dev)
+            rs_oc = torch.arange(0, n_sp * per_sp + 1, per_sp, dtype=torch.int64).to(dev)
+            n_oc = asso.shape[0]
+            nb = _cabi.lib.fgc_oc_workspace_bytes(n_oc)
+            ws_oc = torch.empty(nb, dtype=torch.uint8, device=dev)
+            per_oc = torch.empty(n_sp, dtype=torch.int64, device=dev)
+            st_oc = ctypes.c_int32(0)
+            sz_oc = (ctypes.c_int64 * 3)()
+            stream = _cabi.current_stream(dev)
+
+            def oc_prepare():
+                _cabi.check(_cabi.lib.fgc_oc_prepare(_cabi.ptr(asso), n_oc, _cabi.ptr(rs_oc), n_sp + 1, _cabi.ptr(ws_oc),
+                                                     nb, _cabi.ptr(per_oc), stream), "fgc_oc_prepare")
+
+            oc_prepare()
+            _cabi.check(_cabi.lib.fgc_oc_read_sizes(_cabi.ptr(ws_oc), ctypes.byref(st_oc), sz_oc, stream), "sizes")
+            nu, nq, nr = int(sz_oc[0]), int(sz_oc[1]), int(sz_oc[2])
+            M_oc = torch.empty((nu, nq), dtype=torch.int64, device=dev)
+            Mn_oc = torch.empty((nu, nr), dtype=torch.int64, device=dev)
+
+            def oc_fill():
+                _cabi.check(_cabi.lib.fgc_oc_fill(_cabi.ptr(ws_oc), nb, n_oc, _cabi.ptr(rs_oc), nu, nq, nr,
+                                                  _cabi.ptr(M_oc), _cabi.ptr(Mn_oc), stream), "fgc_oc_fill")
+
+            for _ in range(2):
+                oc_prepare()
+                oc_fill()
+            torch.cuda.synchronize(dev)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            reps = 5
+            t_prep = t_fill = 0.0
+            for _ in range(reps):
+                flush.zero_()
+                ev[0].record()
+                oc_prepare()
+                ev[1].record()
+                oc_fill()
+                ev[2].record()
+                torch.cuda.synchronize(dev)
+                t_prep += ev[0].elapsed_time(ev[1])
+                t_fill += ev[1].elapsed_time(ev[2])
+            fill_bytes = 8 * nu * (nq + nr)
+            oc_local = (t_prep / reps, t_fill / reps, fill_bytes, nu, nq, nr)
+            del M_oc, Mn_oc, ws_oc
+        except Exception as exc:          # noqa: BLE001
+            print("bench.py: oc_helper section failed on rank %d: %r" % (rank, exc), file=sys.stderr)
+        if all_ranks_ok(oc_local is not None):
+            peak_oc, peak_oc_kind = measured_peaks()
+            fill_ms = max_over_ranks(oc_local[1])
+            oc = {"config": "oc_helper_matrices: 16 row splits x 100000 points, truth index uniform in [-20, 200) "
+                            "(200 objects per row split + noise)",
+                  "n_gpus": world, "prepare_ms": max_over_ranks(oc_local[0]), "fill_ms": fill_ms,
+                  "shape": {"n_objects": oc_local[3], "n_max_points_per_object": oc_local[4],
+                            "n_max_points_per_row_split": oc_local[5]},
+                  "roofline": {"bound": "hbm", "kernel": "k_oc_fill_m + k_oc_fill_m_not",
+                               "algorithmic_bytes": oc_local[2],
+                               "achieved": oc_local[2] / (fill_ms * 1e-3) / 1e9, "peak": peak_oc, "unit": "GB/s",
+                               "frac": oc_local[2] / (fill_ms * 1e-3) / 1e9 / peak_oc,
+                               "peak_source": "of " + peak_oc_kind}}
+
     # ---- CPU baseline beside it (rank 0, single-GPU runs only) -----------------------------
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -655,6 +723,8 @@ def run_b200(args):
             line["stacked_gravnet"] = stacked
         if c3:
             line["c3_event_sharded"] = c3
+        if oc:
+            line["oc_helper_matrices"] = oc
         line["phases"] = phases
         print(json.dumps(line), flush=True)
     if world > 1:
