@@ -160,29 +160,49 @@ k_oc_fill_m(const int *__restrict__ vals, const int *__restrict__ obj_start, int
     }
 }
 
+// One warp per tile of kOcTile consecutive columns of one row of M_not.  The j-th non-member is
+// row start + j + t(j), t(j) = number of members with at most j non-members before them; t is
+// non-decreasing in j, so the warp searches it once for the first and once for the last column
+// of the tile (uniform loads) and a column searches only between the two -- in most tiles they
+// are equal and the tile is a plain coalesced store.
+constexpr int kOcTile = 256;
+
 __global__ void __launch_bounds__(256)
 k_oc_fill_m_not(const int *__restrict__ vals, const int *__restrict__ obj_start,
                 const int *__restrict__ obj_split, const int64_t *__restrict__ rs, int64_t n_unique,
                 int64_t n_maxrs, int64_t *__restrict__ M_not)
 {
-    const int64_t total = n_unique * n_maxrs;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
-        const int64_t k = t / n_maxrs, j = t - k * n_maxrs;
+    const int lane = threadIdx.x & 31;
+    const int64_t tiles_per_row = (n_maxrs + kOcTile - 1) / kOcTile;
+    const int64_t n_tiles = n_unique * tiles_per_row;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; tile < n_tiles; tile += n_warps) {
+        const int64_t k = tile / tiles_per_row;
+        const int64_t j0 = (tile - k * tiles_per_row) * kOcTile;
         const int beg = obj_start[k], cnt = obj_start[k + 1] - beg;
         const int e = obj_split[k];
-        const int64_t row_start = rs[e], row_len = rs[e + 1] - row_start;
-        int64_t out = -1;
-        if (j < row_len - cnt) {
-            // number of members whose count of preceding non-members is <= j
-            int lo = 0, hi = cnt;
+        const int64_t row_start = rs[e], n_non = rs[e + 1] - row_start - cnt;
+        const int *__restrict__ members = vals + beg;
+        auto members_up_to = [&](int64_t j, int lo, int hi) {
             while (lo < hi) {
                 const int mid = (lo + hi) >> 1;
-                if ((int64_t)vals[beg + mid] - row_start - mid <= j) lo = mid + 1; else hi = mid;
+                if ((int64_t)members[mid] - row_start - mid <= j) lo = mid + 1; else hi = mid;
             }
-            out = row_start + j + lo;
+            return lo;
+        };
+        const int64_t j_end = j0 + kOcTile < n_maxrs ? j0 + kOcTile : n_maxrs;
+        const int t_first = members_up_to(j0, 0, cnt);
+        const int t_last = members_up_to(j_end - 1, t_first, cnt);
+        int64_t *__restrict__ row = M_not + k * n_maxrs;
+#pragma unroll
+        for (int u = 0; u < kOcTile / 32; u++) {
+            const int64_t j = j0 + lane + 32 * u;
+            if (j < j_end) {
+                int64_t out = -1;
+                if (j < n_non) out = row_start + j + (t_first == t_last ? t_first : members_up_to(j, t_first, t_last));
+                row[j] = out;
+            }
         }
-        M_not[t] = out;
     }
 }
 
@@ -306,8 +326,9 @@ extern "C" int fgc_oc_fill(const void *workspace, size_t workspace_bytes, int64_
         FGC_CHECK_LAUNCH();
     }
     if (out_M_not_or_null && mn_total > 0) {
-        int64_t blocks = ceil_div64(mn_total, 256);
-        if (blocks > 148 * 64) blocks = 148 * 64;
+        const int64_t tiles = n_unique * ceil_div64(n_maxrs, kOcTile);
+        int64_t blocks = ceil_div64(tiles, 8);          // 8 warps per CTA, one tile per warp and pass
+        if (blocks > 148 * 32) blocks = 148 * 32;
         k_oc_fill_m_not<<<(unsigned)blocks, 256, 0, s>>>(vals, obj_start, obj_split, row_splits, n_unique, n_maxrs,
                                                          out_M_not_or_null);
         FGC_CHECK_LAUNCH();
