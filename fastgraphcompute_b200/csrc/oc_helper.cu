@@ -163,44 +163,76 @@ k_oc_fill_m(const int *__restrict__ vals, const int *__restrict__ obj_start, int
 // One warp per tile of kOcTile consecutive columns of one row of M_not.  The j-th non-member is
 // row start + j + t(j), t(j) = number of members with at most j non-members before them; t is
 // non-decreasing in j, so the warp searches it once for the first and once for the last column
-// of the tile (uniform loads) and a column searches only between the two -- in most tiles they
-// are equal and the tile is a plain coalesced store.
-constexpr int kOcTile = 256;
+// of the tile (uniform loads).  With few members inside the tile every column counts them one
+// by one (each raises t by one from its column on), otherwise a column searches between the
+// two bounds.  VEC2: rows are 16-byte aligned (even row length, aligned base) and a lane
+// stores two adjacent columns at once.
+constexpr int kOcTile = 512;
+constexpr int kOcLinear = 16;   // members per tile up to which every column counts them one by one
 
+template <bool VEC2>
 __global__ void __launch_bounds__(256)
 k_oc_fill_m_not(const int *__restrict__ vals, const int *__restrict__ obj_start,
                 const int *__restrict__ obj_split, const int64_t *__restrict__ rs, int64_t n_unique,
-                int64_t n_maxrs, int64_t *__restrict__ M_not)
+                int n_maxrs, int64_t *__restrict__ M_not)
 {
     const int lane = threadIdx.x & 31;
-    const int64_t tiles_per_row = (n_maxrs + kOcTile - 1) / kOcTile;
+    const int tiles_per_row = (n_maxrs + kOcTile - 1) / kOcTile;
     const int64_t n_tiles = n_unique * tiles_per_row;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; tile < n_tiles; tile += n_warps) {
         const int64_t k = tile / tiles_per_row;
-        const int64_t j0 = (tile - k * tiles_per_row) * kOcTile;
+        const int j0 = (int)(tile - k * tiles_per_row) * kOcTile;
         const int beg = obj_start[k], cnt = obj_start[k + 1] - beg;
         const int e = obj_split[k];
-        const int64_t row_start = rs[e], n_non = rs[e + 1] - row_start - cnt;
+        const int64_t row_start = rs[e];
+        const int n_non = (int)(rs[e + 1] - row_start) - cnt;
+        // member i (a global point id) has  members[i] - row_start - i  non-members before it
         const int *__restrict__ members = vals + beg;
-        auto members_up_to = [&](int64_t j, int lo, int hi) {
+        const int rs32 = (int)row_start;
+        auto members_up_to = [&](int j, int lo, int hi) {
             while (lo < hi) {
                 const int mid = (lo + hi) >> 1;
-                if ((int64_t)members[mid] - row_start - mid <= j) lo = mid + 1; else hi = mid;
+                if (members[mid] - rs32 - mid <= j) lo = mid + 1; else hi = mid;
             }
             return lo;
         };
-        const int64_t j_end = j0 + kOcTile < n_maxrs ? j0 + kOcTile : n_maxrs;
+        const int j_end = j0 + kOcTile < n_maxrs ? j0 + kOcTile : n_maxrs;
         const int t_first = members_up_to(j0, 0, cnt);
         const int t_last = members_up_to(j_end - 1, t_first, cnt);
-        int64_t *__restrict__ row = M_not + k * n_maxrs;
+        int64_t *__restrict__ row = M_not + k * (int64_t)n_maxrs;
+        constexpr int PER = kOcTile / 32;           // columns per lane
+        // column of slot u of this lane
+        auto column = [&](int u) { return VEC2 ? j0 + 2 * lane + 64 * (u >> 1) + (u & 1) : j0 + lane + 32 * u; };
+        int t_of[PER];
+        if (t_last - t_first <= kOcLinear) {
 #pragma unroll
-        for (int u = 0; u < kOcTile / 32; u++) {
-            const int64_t j = j0 + lane + 32 * u;
-            if (j < j_end) {
-                int64_t out = -1;
-                if (j < n_non) out = row_start + j + (t_first == t_last ? t_first : members_up_to(j, t_first, t_last));
-                row[j] = out;
+            for (int u = 0; u < PER; u++) t_of[u] = t_first;
+            for (int t = t_first; t < t_last; t++) {
+                const int b = members[t] - rs32 - t;
+#pragma unroll
+                for (int u = 0; u < PER; u++) t_of[u] += column(u) >= b ? 1 : 0;
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < PER; u++) t_of[u] = members_up_to(column(u), t_first, t_last);
+        }
+        if (VEC2) {
+#pragma unroll
+            for (int u = 0; u < PER; u += 2) {
+                const int j = column(u);
+                if (j < j_end) {    // j_end is even here, so j + 1 < j_end as well
+                    longlong2 v;
+                    v.x = j < n_non ? row_start + j + t_of[u] : -1;
+                    v.y = j + 1 < n_non ? row_start + j + 1 + t_of[u + 1] : -1;
+                    *reinterpret_cast<longlong2 *>(row + j) = v;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < PER; u++) {
+                const int j = column(u);
+                if (j < j_end) row[j] = j < n_non ? row_start + j + t_of[u] : -1;
             }
         }
     }
@@ -326,11 +358,16 @@ extern "C" int fgc_oc_fill(const void *workspace, size_t workspace_bytes, int64_
         FGC_CHECK_LAUNCH();
     }
     if (out_M_not_or_null && mn_total > 0) {
+        if (n_maxrs > 0x7fffffff) return FGC_ERR_TOO_LARGE;
         const int64_t tiles = n_unique * ceil_div64(n_maxrs, kOcTile);
         int64_t blocks = ceil_div64(tiles, 8);          // 8 warps per CTA, one tile per warp and pass
         if (blocks > 148 * 32) blocks = 148 * 32;
-        k_oc_fill_m_not<<<(unsigned)blocks, 256, 0, s>>>(vals, obj_start, obj_split, row_splits, n_unique, n_maxrs,
-                                                         out_M_not_or_null);
+        if ((n_maxrs & 1) == 0 && ((uintptr_t)out_M_not_or_null & 15) == 0)
+            k_oc_fill_m_not<true><<<(unsigned)blocks, 256, 0, s>>>(vals, obj_start, obj_split, row_splits, n_unique,
+                                                                   (int)n_maxrs, out_M_not_or_null);
+        else
+            k_oc_fill_m_not<false><<<(unsigned)blocks, 256, 0, s>>>(vals, obj_start, obj_split, row_splits, n_unique,
+                                                                    (int)n_maxrs, out_M_not_or_null);
         FGC_CHECK_LAUNCH();
     }
     return FGC_OK;
