@@ -160,15 +160,17 @@ k_oc_fill_m(const int *__restrict__ vals, const int *__restrict__ obj_start, int
     }
 }
 
-// One warp per tile of kOcTile consecutive columns of one row of M_not.  The j-th non-member is
-// row start + j + t(j), t(j) = number of members with at most j non-members before them; t is
-// non-decreasing in j, so the warp searches it once for the first and once for the last column
-// of the tile (uniform loads).  With few members inside the tile every column counts them one
-// by one (each raises t by one from its column on), otherwise a column searches between the
-// two bounds.  VEC2: rows are 16-byte aligned (even row length, aligned base) and a lane
-// stores two adjacent columns at once.
+// M_not, one warp per run of kOcRun tiles of kOcTile consecutive columns of one row.  The j-th
+// non-member is  row start + j + t(j),  t(j) = number of members with at most j non-members
+// before them.  t is non-decreasing in j: the warp searches it once for the first column of
+// its run (uniform loads) and then walks the member list forward, tile by tile -- every member
+// that falls into the tile raises t by one from its column on.  A tile with more than
+// kOcLinear members (a dense object) lets every column search between the tile's bounds
+// instead.  VEC2: rows are 16-byte aligned (even row length, aligned base) and a lane stores
+// two adjacent columns at once.
 constexpr int kOcTile = 512;
-constexpr int kOcLinear = 16;   // members per tile up to which every column counts them one by one
+constexpr int kOcRun = 4;
+constexpr int kOcLinear = 16;
 
 template <bool VEC2>
 __global__ void __launch_bounds__(256)
@@ -177,12 +179,13 @@ k_oc_fill_m_not(const int *__restrict__ vals, const int *__restrict__ obj_start,
                 int n_maxrs, int64_t *__restrict__ M_not)
 {
     const int lane = threadIdx.x & 31;
-    const int tiles_per_row = (n_maxrs + kOcTile - 1) / kOcTile;
-    const int64_t n_tiles = n_unique * tiles_per_row;
+    constexpr int kSpan = kOcTile * kOcRun;
+    const int runs_per_row = (n_maxrs + kSpan - 1) / kSpan;
+    const int64_t n_runs = n_unique * runs_per_row;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    for (int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; tile < n_tiles; tile += n_warps) {
-        const int64_t k = tile / tiles_per_row;
-        const int j0 = (int)(tile - k * tiles_per_row) * kOcTile;
+    for (int64_t run = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5; run < n_runs; run += n_warps) {
+        const int64_t k = run / runs_per_row;
+        const int run0 = (int)(run - k * runs_per_row) * kSpan;
         const int beg = obj_start[k], cnt = obj_start[k + 1] - beg;
         const int e = obj_split[k];
         const int64_t row_start = rs[e];
@@ -197,43 +200,46 @@ k_oc_fill_m_not(const int *__restrict__ vals, const int *__restrict__ obj_start,
             }
             return lo;
         };
-        const int j_end = j0 + kOcTile < n_maxrs ? j0 + kOcTile : n_maxrs;
-        const int t_first = members_up_to(j0, 0, cnt);
-        const int t_last = members_up_to(j_end - 1, t_first, cnt);
         int64_t *__restrict__ row = M_not + k * (int64_t)n_maxrs;
-        constexpr int PER = kOcTile / 32;           // columns per lane
-        // column of slot u of this lane
-        auto column = [&](int u) { return VEC2 ? j0 + 2 * lane + 64 * (u >> 1) + (u & 1) : j0 + lane + 32 * u; };
-        int t_of[PER];
-        if (t_last - t_first <= kOcLinear) {
+        int t_first = members_up_to(run0, 0, cnt);
+        for (int j0 = run0; j0 < run0 + kSpan && j0 < n_maxrs; j0 += kOcTile) {
+            const int j_end = j0 + kOcTile < n_maxrs ? j0 + kOcTile : n_maxrs;
+            constexpr int PER = kOcTile / 32;           // columns per lane
+            auto column = [&](int u) { return VEC2 ? j0 + 2 * lane + 64 * (u >> 1) + (u & 1) : j0 + lane + 32 * u; };
+            int t_of[PER];
 #pragma unroll
             for (int u = 0; u < PER; u++) t_of[u] = t_first;
-            for (int t = t_first; t < t_last; t++) {
+            int t = t_first;
+            for (; t < cnt && t - t_first <= kOcLinear; t++) {
                 const int b = members[t] - rs32 - t;
+                if (b >= j_end) break;
 #pragma unroll
                 for (int u = 0; u < PER; u++) t_of[u] += column(u) >= b ? 1 : 0;
             }
-        } else {
+            if (t - t_first > kOcLinear) {
+                t = members_up_to(j_end - 1, t, cnt);
 #pragma unroll
-            for (int u = 0; u < PER; u++) t_of[u] = members_up_to(column(u), t_first, t_last);
-        }
-        if (VEC2) {
+                for (int u = 0; u < PER; u++) t_of[u] = members_up_to(column(u), t_first, t);
+            }
+            if (VEC2) {
 #pragma unroll
-            for (int u = 0; u < PER; u += 2) {
-                const int j = column(u);
-                if (j < j_end) {    // j_end is even here, so j + 1 < j_end as well
-                    longlong2 v;
-                    v.x = j < n_non ? row_start + j + t_of[u] : -1;
-                    v.y = j + 1 < n_non ? row_start + j + 1 + t_of[u + 1] : -1;
-                    *reinterpret_cast<longlong2 *>(row + j) = v;
+                for (int u = 0; u < PER; u += 2) {
+                    const int j = column(u);
+                    if (j < j_end) {    // j_end is even here, so j + 1 < j_end as well
+                        longlong2 v;
+                        v.x = j < n_non ? row_start + j + t_of[u] : -1;
+                        v.y = j + 1 < n_non ? row_start + j + 1 + t_of[u + 1] : -1;
+                        *reinterpret_cast<longlong2 *>(row + j) = v;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < PER; u++) {
+                    const int j = column(u);
+                    if (j < j_end) row[j] = j < n_non ? row_start + j + t_of[u] : -1;
                 }
             }
-        } else {
-#pragma unroll
-            for (int u = 0; u < PER; u++) {
-                const int j = column(u);
-                if (j < j_end) row[j] = j < n_non ? row_start + j + t_of[u] : -1;
-            }
+            t_first = t;
         }
     }
 }
@@ -359,8 +365,8 @@ extern "C" int fgc_oc_fill(const void *workspace, size_t workspace_bytes, int64_
     }
     if (out_M_not_or_null && mn_total > 0) {
         if (n_maxrs > 0x7fffffff) return FGC_ERR_TOO_LARGE;
-        const int64_t tiles = n_unique * ceil_div64(n_maxrs, kOcTile);
-        int64_t blocks = ceil_div64(tiles, 8);          // 8 warps per CTA, one tile per warp and pass
+        const int64_t runs = n_unique * ceil_div64(n_maxrs, kOcTile * kOcRun);
+        int64_t blocks = ceil_div64(runs, 8);           // 8 warps per CTA, one run of tiles per warp and pass
         if (blocks > 148 * 32) blocks = 148 * 32;
         if ((n_maxrs & 1) == 0 && ((uintptr_t)out_M_not_or_null & 15) == 0)
             k_oc_fill_m_not<true><<<(unsigned)blocks, 256, 0, s>>>(vals, obj_start, obj_split, row_splits, n_unique,
