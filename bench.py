@@ -234,6 +234,8 @@ def run_b200(args):
     import importlib
     knn_mod = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
 
+    sections = set() if args.no_gravnet else {x for x in args.sections.split(",") if x and x != "none"}
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -444,7 +446,7 @@ def run_b200(args):
 
     # ---- GravNet layer (second half of the headline metric) -------------------------------
     gravnet = None
-    if not args.no_gravnet:
+    if "gravnet" in sections:
         from fastgraphcompute_b200.gnn_ops import GravNetOp
         gw = synthetic.c4_gravnet(seed=rank)
         m = synthetic.init_gravnet_weights(
@@ -493,7 +495,7 @@ def run_b200(args):
     # propagate 32, space 4, hidden 128, 10 outputs; one step = forward, sum(output)*0 backward,
     # SGD step, on a fresh randn input of n_nodes points in one event; largest size of its sweep)
     stacked = None
-    if not args.no_gravnet:
+    if "stacked" in sections:
         n_nodes = 200000
         s_local = None
         try:
@@ -539,7 +541,7 @@ def run_b200(args):
     # collective) and, with more than one rank, gathers the rows of all ranks (the one
     # exchange step of the multi-GPU path).
     c3 = None
-    if not args.no_gravnet:
+    if "c3" in sections:
         c3_local = None
         c3_reps = 3
         try:
@@ -593,7 +595,7 @@ def run_b200(args):
 
     # ---- object-condensation index matrices (the loss-side consumer of the same row splits) --
     oc = None
-    if not args.no_gravnet:
+    if "oc" in sections:
         oc_local = None
         try:
             import ctypes
@@ -737,7 +739,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--no-gravnet", action="store_true")
+    ap.add_argument("--no-gravnet", action="store_true", help="headline workload only (same as --sections none)")
+    ap.add_argument("--sections", default="gravnet,stacked,c3,oc",
+                    help="additional workloads to time after the headline one: any of gravnet, stacked, c3, oc")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
