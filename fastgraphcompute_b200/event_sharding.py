@@ -186,3 +186,28 @@ def sharded_binned_select_knn(K, coords, row_splits, direction=None, torch_compa
         return rows, idx, dsq
     full_idx, full_dsq = gather_rows(rows, [idx, dsq], coords.shape[0], part.points, group)
     return full_idx, full_dsq
+
+
+def allreduce_gradients(parameters, group=None):
+    """Sum the gradients of ``parameters`` over the ranks in ONE all-reduce.
+
+    The exchange step of data-parallel training over event shards: every rank runs forward and
+    backward on its own events (same module weights everywhere), the parameter gradients -- a
+    few thousand floats for a GravNet layer -- are flattened into one buffer, summed over the
+    ranks and written back, so that every rank holds the gradient of the whole batch.
+    Parameters without a gradient count as zero."""
+    params = [p for p in parameters]
+    if not params:
+        return
+    flat = torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).reshape(-1).to(torch.float32)
+                      for p in params])
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+    off = 0
+    for p in params:
+        n = p.numel()
+        g = flat[off: off + n].view_as(p).to(p.dtype)
+        if p.grad is None:
+            p.grad = g.clone()
+        else:
+            p.grad.copy_(g)
+        off += n

@@ -116,3 +116,44 @@ def test_two_rank_gloo(fail_rank):
         assert dict(out) == {0: "ok", 1: "ok"}
     else:
         assert out[fail_rank].startswith("raised")
+
+
+def _grad_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(5, 7), torch.nn.ReLU(), torch.nn.Linear(7, 2))
+        frozen = torch.nn.Parameter(torch.zeros(3))           # never used: no gradient
+        g = torch.Generator().manual_seed(3)
+        x = torch.randn((90, 5), generator=g)
+        rs = torch.tensor([0, 20, 50, 50, 90])
+        part = es.partition_events(rs, world)
+        rows, _ = es.shard_rows(rs, part.events[rank])
+        (model(x[rows]) ** 2).sum().backward()
+        es.allreduce_gradients(list(model.parameters()) + [frozen])
+        ref = torch.nn.Sequential(torch.nn.Linear(5, 7), torch.nn.ReLU(), torch.nn.Linear(7, 2))
+        ref.load_state_dict(model.state_dict())
+        (ref(x) ** 2).sum().backward()
+        ok = all(torch.allclose(a.grad, b.grad, rtol=1e-5, atol=1e-6)
+                 for a, b in zip(model.parameters(), ref.parameters()))
+        out[rank] = "ok" if ok and bool((frozen.grad == 0).all()) else "mismatch"
+    finally:
+        dist.destroy_process_group()
+
+
+def test_allreduce_gradients_two_rank_gloo():
+    """Data-parallel step over event shards: summed parameter gradients == whole-batch gradients."""
+    world = 2
+    port = _free_port()
+    mgr = mp.Manager()
+    out = mgr.dict()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_grad_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert dict(out) == {0: "ok", 1: "ok"}

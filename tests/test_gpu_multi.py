@@ -39,7 +39,25 @@ def _worker(rank, world, port, out):
         same = torch.equal(torch.sort(dsq, 1).values, torch.sort(ref_dsq, 1).values) and \
             torch.equal(torch.sort(idx, 1).values, torch.sort(ref_idx, 1).values)
         part = es.partition_events(w.row_splits, world)
-        out[rank] = "ok" if same and sum(part.points) == w.n_points else "mismatch"
+        # data-parallel GravNet step over the event shards: summed parameter gradients must equal
+        # the gradients of the whole batch on one GPU
+        from fastgraphcompute_b200.gnn_ops import GravNetOp
+        gw = synthetic.c4_gravnet(scale=0.02, n_events=6)
+        gpart = es.partition_events(gw.row_splits, world)
+        torch.manual_seed(0)
+        layer = synthetic.init_gravnet_weights(
+            GravNetOp(gw.in_channels, gw.out_channels, gw.space_dimensions, gw.propagate_dimensions, gw.k)).to(dev)
+        x = gw.x.to(dev)
+        rows, local_rs = es.shard_rows(gw.row_splits, gpart.events[rank], device=dev)
+        (layer(x.index_select(0, rows), local_rs)[0] ** 2).sum().backward()
+        es.allreduce_gradients(layer.parameters())
+        mine = [p.grad.clone() for p in layer.parameters()]
+        layer.zero_grad(set_to_none=True)
+        (layer(x, gw.row_splits.to(dev))[0] ** 2).sum().backward()
+        grads_ok = all(float((a - p.grad).abs().max()) <= 2e-4 * (float(p.grad.abs().max()) + 1e-30)
+                       for a, p in zip(mine, layer.parameters()) if p.dim() > 1)
+        out[rank] = "ok" if same and grads_ok and sum(part.points) == w.n_points else (
+            "mismatch knn=%s grads=%s" % (same, grads_ok))
     finally:
         dist.destroy_process_group()
 
