@@ -12,7 +12,8 @@ from .extensions.bin_by_coordinates import bin_by_coordinates
 from .extensions.binned_select_knn import binned_select_knn
 from .extensions.index_replacer import index_replacer
 from .extensions.oc_helper import oc_helper_matrices, select_with_default
+from .extensions.select_knn import select_knn
 
 __version__ = "0.1.0"
 __all__ = ["bin_by_coordinates", "binned_select_knn", "index_replacer", "select_with_default",
-           "oc_helper_matrices"]
+           "oc_helper_matrices", "select_knn"]

@@ -108,6 +108,7 @@ SIGNATURES = {
                                                         c_void_p, c_i64, c_i32, c_i32, c_void_p, c_size,
                                                         c_void_p, c_void_p, c_void_p, c_void_p]),
     "fgc_knn_cell_order": (c_void_p, [c_void_p, c_i64, c_i32, c_i64, c_i32]),
+    "fgc_knn_radius_filter": (ctypes.c_int, [c_void_p, c_void_p, c_i64, c_i32, ctypes.c_double, c_i32, c_void_p]),
     "fgc_oc_workspace_bytes": (c_size, [c_i64]),
     "fgc_oc_prepare": (ctypes.c_int, [c_void_p, c_i64, c_void_p, c_i64, c_void_p, c_size, c_void_p, c_void_p]),
     "fgc_oc_read_sizes": (ctypes.c_int, [c_void_p, ctypes.POINTER(c_i32), ctypes.POINTER(c_i64), c_void_p]),

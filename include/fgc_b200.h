@@ -321,6 +321,18 @@ int fgc_gravnet_aggregate_bwd_sorted(const float *prop, const int64_t *idx, cons
                                      fgc_stream_t stream);
 
 /*
+ * Radius mode of the reference's brute-force op select_knn::select_knn(coords, row_splits, mask,
+ * n_neighbours, max_radius, mask_mode) (select_knn.cpp:60-62; select_knn_cpu.cpp:98-132 /
+ * select_knn_cuda_kernel.cu:73-132; the mask arguments are never read there): the K-1 nearest
+ * other points of the row split that lie within max_radius.  Run fgc_binned_knn_fwd, then this
+ * call on its outputs, in place: slots with distsq > max_radius^2 are dropped, the remaining
+ * slots close up in their order, freed slots become pads.  max_radius <= 0: no radius, no-op.
+ * The radius is squared in double and rounded to float once (select_knn_cpu.cpp:176-178).
+ */
+int fgc_knn_radius_filter(int64_t *idx, float *distsq, int64_t n_vert, int32_t K, double max_radius,
+                          int32_t tf_compat, fgc_stream_t stream);
+
+/*
  * Object-condensation index matrices -- the consumers of the same row_splits data on the loss
  * side (the reference's oc_helper_matrices: extensions/oc_helper.py:128-230 ->
  * oc_helper_cpu.cpp:117-156 / oc_helper_cuda_kernel.cu, helper oc_helper_helper.cpp:31-93).

@@ -25,7 +25,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 OUT_SO = os.path.join(OUT_DIR, "binned_knn_ops.so")
 # single-file op libraries of the loss-side helpers (setup.py:139-159 of the reference)
-EXTRA_LIBS = {"oc_helper_cpu.so": ["oc_helper_cpu.cpp"], "oc_helper_helper.so": ["oc_helper_helper.cpp"]}
+EXTRA_LIBS = {"oc_helper_cpu.so": ["oc_helper_cpu.cpp"], "oc_helper_helper.so": ["oc_helper_helper.cpp"],
+              # brute-force kNN (setup.py:116-129); its CUDA twin is replaced by a stub
+              "select_knn_lib.so": ["select_knn.cpp", "select_knn_cpu.cpp", "@ref_cuda_stubs.cpp"]}
 
 CPU_SOURCES = [
     "binned_knn_autograd_kernel.cpp",
@@ -54,7 +56,8 @@ def build(reference_root=None, force=False, verbose=True):
     srcs.append(os.path.join(HERE, "ref_cuda_stubs.cpp"))
     targets = {OUT_SO: srcs}
     for name, files in EXTRA_LIBS.items():
-        targets[os.path.join(OUT_DIR, name)] = [os.path.join(ext_dir, f) for f in files]
+        targets[os.path.join(OUT_DIR, name)] = [os.path.join(HERE, f[1:]) if f.startswith("@")
+                                                else os.path.join(ext_dir, f) for f in files]
     stale = {so: ss for so, ss in targets.items()
              if force or not os.path.exists(so) or any(os.path.getmtime(so) < os.path.getmtime(x) for x in ss)}
     if not stale:

@@ -151,6 +151,21 @@ def select_with_default(idx, feat, default_value):
     return out
 
 
+def select_knn(K, coords, row_splits, max_radius=-1.0):
+    """Oracle for the reference's brute-force op select_knn::select_knn (select_knn.cpp:60-62,
+    select_knn_cpu.cpp:9-206): (idx [N,K] i64, distsq [N,K] f32); max_radius <= 0: no radius."""
+    L = _lib()
+    c = np.ascontiguousarray(coords, dtype=np.float32)
+    rs = np.ascontiguousarray(row_splits, dtype=np.int64)
+    N, D = c.shape
+    idx = np.zeros((N, K), np.int64)
+    dist = np.zeros((N, K), np.float32)
+    r2 = np.float32(float(max_radius) * float(max_radius)) if max_radius > 0 else np.float32(max_radius)
+    L.oracle_select_knn(_f(c), _i(rs), _c64(len(rs)), _c64(N), _c64(K), _c64(D), ctypes.c_float(float(r2)),
+                        _i(idx), _f(dist))
+    return idx, dist
+
+
 def oc_helper_matrices(truth_idxs, row_splits, calc_m_not=True):
     """Oracle for oc_helper_matrices (extensions/oc_helper.py:128-230): the unique
     (truth index, row split) pairs with a non-negative index (oc_helper.py:100-118), the two

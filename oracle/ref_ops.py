@@ -184,3 +184,28 @@ def ref_oc_helper_matrices(truth_idxs, row_splits, calc_m_not=True):
         truth_idxs.contiguous(), unique_idxs, unique_rs, row_splits.contiguous(),
         max_same.to(torch.int64).reshape(1), max_length.reshape(1), bool(calc_m_not))
     return M, M_not, per_split
+
+
+# --------------------------------------------------------------------------- brute-force select_knn
+
+_SELECT_SO = os.path.join(_HERE, "_ref", "select_knn_lib.so")
+_select_loaded = False
+
+
+def select_knn_available():
+    return os.path.exists(_SELECT_SO)
+
+
+def ref_select_knn(K, coords, row_splits, max_radius=-1.0):
+    """The reference's brute-force op select_knn::select_knn on CPU tensors (select_knn.cpp:60-62
+    -> select_knn_cpu.cpp:161-206).  The mask arguments are passed as the op wants them; its CPU
+    kernel never reads them."""
+    global _select_loaded
+    if not _select_loaded:
+        if not select_knn_available():
+            raise RuntimeError("oracle/_ref/select_knn_lib.so missing: run python oracle/build_ref.py")
+        torch.ops.load_library(_SELECT_SO)
+        _select_loaded = True
+    mask = torch.zeros(coords.shape[0], dtype=torch.int64)
+    return torch.ops.select_knn.select_knn(coords.to(torch.float32).contiguous(), row_splits.to(torch.int64).contiguous(),
+                                           mask, int(K), float(max_radius), 0)

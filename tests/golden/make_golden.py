@@ -3,8 +3,8 @@
     python oracle/build_ref.py && python tests/golden/make_golden.py
 
 Needs oracle/_ref/binned_knn_ops.so (built from the unmodified reference
-sources).  Writes tests/golden/{knn,binning,gravnet,misc,stacked,oc}.npz
-(`python make_golden.py stacked` / `oc` write only that file).  The tests only
+sources).  Writes tests/golden/{knn,binning,gravnet,misc,stacked,oc,select}.npz
+(`python make_golden.py stacked` / `oc` / `select` write only that file).  The tests only
 read those files; they never need the reference checkout.
 """
 import os
@@ -112,8 +112,32 @@ def make_oc():
     print("oc done")
 
 
+def make_select():
+    """The reference's brute-force op select_knn::select_knn (select_knn_cpu.cpp) with and
+    without a radius, on small seeded cases."""
+    rng = np.random.RandomState(91)
+    store = {}
+    for name, sizes, d, k, r in (("no_radius", [60, 90], 3, 8, -1.0), ("radius_small", [150], 3, 12, 0.12),
+                                 ("radius_mid_d4", [80, 5, 120], 4, 20, 0.35), ("radius_large", [70, 70], 2, 6, 10.0),
+                                 ("fewer_points_than_k", [4, 9], 3, 12, 0.5)):
+        rs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+        c = rng.rand(int(rs[-1]), d).astype(np.float32)
+        idx, dist = ref_ops.ref_select_knn(k, torch.tensor(c), torch.tensor(rs), r)
+        store[name + "/in/coords"] = c
+        store[name + "/in/row_splits"] = rs
+        store[name + "/in/K"] = np.asarray(k)
+        store[name + "/in/max_radius"] = np.asarray(r)
+        store[name + "/out/idx"] = idx.numpy().astype(np.int32)
+        store[name + "/out/distsq"] = dist.numpy()
+    np.savez_compressed(os.path.join(HERE, "select.npz"), **store)
+    print("select done")
+
+
 def main():
     torch.set_num_threads(1)
+    if "select" in sys.argv[1:]:
+        make_select()
+        return
     if "stacked" in sys.argv[1:]:
         make_stacked()
         return
@@ -197,6 +221,7 @@ def main():
     print("misc done")
     make_stacked()
     make_oc()
+    make_select()
 
 
 if __name__ == "__main__":

@@ -253,3 +253,29 @@ def test_oc_helper_live_reference():
         rM, rM_not, rper = ref_ops.ref_oc_helper_matrices(torch.tensor(asso), torch.tensor(rs))
         assert np.array_equal(M, rM.numpy()) and np.array_equal(M_not, rM_not.numpy())
         assert np.array_equal(per, rper.numpy())
+
+
+# ---- brute-force select_knn with a radius -----------------------------------------------------
+
+def test_select_knn_golden(golden_dir):
+    for name, c in load(golden_dir, "select").items():
+        i = c["in"]
+        idx, dist = oracle.select_knn(int(i["K"]), i["coords"], i["row_splits"], float(i["max_radius"]))
+        assert np.array_equal(idx, c["out"]["idx"].astype(np.int64)), name     # slot order included
+        assert np.array_equal(dist, c["out"]["distsq"]), name
+
+
+def test_select_knn_live_reference():
+    from oracle import ref_ops
+    if not ref_ops.select_knn_available():
+        pytest.skip("oracle/_ref/select_knn_lib.so not built (needs the reference checkout)")
+    import torch
+    rng = np.random.RandomState(17)
+    for trial in range(8):
+        n = int(rng.randint(5, 200))
+        c = rng.rand(n, int(rng.randint(2, 5))).astype(np.float32)
+        rs = np.array([0, n // 3, n], np.int64)
+        k, r = int(rng.choice([2, 7, 16])), float(rng.choice([-1.0, 0.2, 0.5]))
+        idx, dist = oracle.select_knn(k, c, rs, r)
+        ri, rd = ref_ops.ref_select_knn(k, torch.tensor(c), torch.tensor(rs), r)
+        assert np.array_equal(idx, ri.numpy()) and np.array_equal(dist, rd.numpy())
