@@ -666,6 +666,44 @@ def run_b200(args):
                                "frac": oc_local[2] / (fill_ms * 1e-3) / 1e9 / peak_oc,
                                "peak_source": "of " + peak_oc_kind}}
 
+    # ---- the reference's own published kNN timings, same configurations ------------------------
+    # (forward only, one event, timer around the public call plus a device
+    # synchronise as in performance/generate_faiss_performance.py:68-92; the published figures
+    # come from an unspecified GPU and are quoted for orientation, not as a like-for-like ratio)
+    published = None
+    if "published" in sections and rank == 0:
+        try:
+            rows = []
+            for tag, n_p, d_p, k_p, ref_ms, src in (
+                    ("K=40 D=5 N=100000 randn", 100000, 5, 40, 72.3, "performance/faiss_data_sizes.csv:20"),
+                    ("K=40 D=5 N=1000000 randn", 1000000, 5, 40, 2035.0, "performance/faiss_data_sizes.csv:33"),
+                    ("K=40 D=5 N=3000000 randn", 3000000, 5, 40, 13288.0, "performance/faiss_data_sizes.csv:43"),
+                    ("K=40 D=4 N=1000000 randn", 1000000, 4, 40, 993.6, "graphing/master_data.csv:668"),
+                    ("K=40 D=4 N=5000000 randn", 5000000, 4, 40, 10232.0, "graphing/master_data.csv:1477"),
+                    ("K=40 D=3 N=700000 randn", 700000, 3, 40, 148.5, "graphing/master_data.csv:566")):
+                gp = torch.Generator().manual_seed(42)
+                cp = torch.randn((n_p, d_p), generator=gp).to(dev)
+                rp = torch.tensor([0, n_p], dtype=torch.int64, device=dev)
+                for _ in range(2):
+                    fgc.binned_select_knn(k_p, cp, rp)
+                torch.cuda.synchronize(dev)
+                ts = []
+                for _ in range(3):
+                    t0 = time.perf_counter()
+                    out_p = fgc.binned_select_knn(k_p, cp, rp)
+                    torch.cuda.synchronize(dev)
+                    ts.append(1e3 * (time.perf_counter() - t0))
+                    del out_p
+                rows.append({"config": tag, "forward_ms": statistics.median(ts), "reference_published_ms": ref_ms,
+                             "reference_source": src})
+                del cp
+            published = {"method": "wall clock around binned_select_knn + synchronize, median of 3 after 2 warm-ups, "
+                                   "standard-normal coordinates, one row split",
+                         "note": "published figures: the reference's CUDA path on an unspecified GPU",
+                         "rows": rows}
+        except Exception as exc:          # noqa: BLE001
+            print("bench.py: published-config section failed: %r" % (exc,), file=sys.stderr)
+
     # ---- CPU baseline beside it (rank 0, single-GPU runs only) -----------------------------
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -732,6 +770,8 @@ def run_b200(args):
             line["c3_event_sharded"] = c3
         if oc:
             line["oc_helper_matrices"] = oc
+        if published:
+            line["published_configs"] = published
         line["phases"] = phases
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -745,8 +785,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-gravnet", action="store_true", help="headline workload only (same as --sections none)")
-    ap.add_argument("--sections", default="gravnet,stacked,c3,oc",
-                    help="additional workloads to time after the headline one: any of gravnet, stacked, c3, oc")
+    ap.add_argument("--sections", default="gravnet,stacked,c3,oc,published",
+                    help="additional workloads to time after the headline one: any of gravnet, stacked, c3, oc, published")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
