@@ -731,7 +731,7 @@ def run_b200(args):
         d = w.coords.shape[1]
         alg_bytes = n * (4 * d + 8 * K + 4 * K)          # coords read + int64 idx + fp32 distsq written
         achieved = alg_bytes / (knn_ms_avg * 1e-3) / 1e9
-        launches_per_step = (_cabi.KERNELS_BUILD_GRID + _cabi.KERNELS_PUBLISH_STATUS + _cabi.KERNELS_SEARCH +
+        launches_per_step = (_cabi.KERNELS_BUILD_GRID_D4 + _cabi.KERNELS_PUBLISH_STATUS + _cabi.KERNELS_SEARCH +
                              _cabi.KERNELS_KNN_BWD)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,

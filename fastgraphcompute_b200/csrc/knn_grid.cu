@@ -3,12 +3,15 @@
 //
 // Pipeline (all on the caller's stream, no host synchronisation):
 //   k_minmax      fused finite check + min/max of the binned coordinates
-//   k_grid_setup  cell width / grid shape from the extents and the point count
+//   k_grid_setup  cell width / grid shape from the extents and the point count; the grid spans
+//                 the first min(D, 4) coordinates
 //   k_zero_counts clear the cell table
 //   k_histogram   cell id per point, warp-aggregated atomic histogram; the value
 //                 returned by the atomic is the point's rank inside its cell
 //   k_scan_*      exclusive scan of the histogram -> cell boundaries
-//   k_cell_stat_refine   density pass: shrink the cells where the data is clustered
+//   k_cell_stat_refine   density pass: shrink the cells where the data is clustered; D = 4 data
+//                 that is strongly clustered goes back to a grid over three coordinates and
+//                 gets a second density pass there
 //   k_fill_ids    counting-sort scatter of the original ids into cell order (arbitrary inside a cell)
 //   k_rank_place  ids in ascending order inside every cell (the layout is the same on every
 //                 run); coordinates (padded to float4), cell id and direction flag in that order
@@ -38,7 +41,7 @@ namespace fgc {
 __global__ void __launch_bounds__(256)
 k_minmax(const float *__restrict__ coords, int n_vert, int n_coords, int n_bin_dims, KnnGrid *g)
 {
-    uint32_t lmin[3] = {0, 0, 0}, lmax[3] = {0, 0, 0};
+    uint32_t lmin[4] = {0, 0, 0, 0}, lmax[4] = {0, 0, 0, 0};
     uint32_t bad = 0;
     for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vert; v += gridDim.x * blockDim.x) {
         const float *row = coords + (size_t)v * n_coords;
@@ -48,24 +51,24 @@ k_minmax(const float *__restrict__ coords, int n_vert, int n_coords, int n_bin_d
             if (c < n_bin_dims) {
                 const uint32_t k = float_to_ordered(x);
 #pragma unroll
-                for (int cc = 0; cc < 3; cc++)
+                for (int cc = 0; cc < 4; cc++)
                     if (cc == c) { lmin[cc] = max(lmin[cc], ~k); lmax[cc] = max(lmax[cc], k); }
             }
         }
     }
-    __shared__ uint32_t s_min[3], s_max[3], s_bad;
-    if (threadIdx.x < 3) { s_min[threadIdx.x] = 0; s_max[threadIdx.x] = 0; }
+    __shared__ uint32_t s_min[4], s_max[4], s_bad;
+    if (threadIdx.x < 4) { s_min[threadIdx.x] = 0; s_max[threadIdx.x] = 0; }
     if (threadIdx.x == 0) s_bad = 0;
     __syncthreads();
 #pragma unroll
-    for (int c = 0; c < 3; c++) {
+    for (int c = 0; c < 4; c++) {
         const uint32_t a = __reduce_max_sync(FGC_FULL_MASK, lmin[c]);
         const uint32_t b = __reduce_max_sync(FGC_FULL_MASK, lmax[c]);
         if ((threadIdx.x & 31) == 0) { atomicMax(&s_min[c], a); atomicMax(&s_max[c], b); }
     }
     if (__any_sync(FGC_FULL_MASK, bad) && (threadIdx.x & 31) == 0) atomicOr(&s_bad, 1u);
     __syncthreads();
-    if (threadIdx.x < 3) {
+    if (threadIdx.x < 4) {
         atomicMax(&g->min_key[threadIdx.x], s_min[threadIdx.x]);
         atomicMax(&g->max_key[threadIdx.x], s_max[threadIdx.x]);
     }
@@ -73,13 +76,13 @@ k_minmax(const float *__restrict__ coords, int n_vert, int n_coords, int n_bin_d
 }
 
 // Cells per dimension for a wanted cell width; widens the cells until the table fits.
-__device__ inline void fit_shape(const float (&ext)[3], double wd, int bins_cap, int (&n)[3], float &w)
+__device__ inline void fit_shape(const float (&ext)[4], double wd, int bins_cap, int (&n)[4], float &w)
 {
     for (int iter = 0; iter < 400; iter++) {
         w = (float)wd;
         const float inv = __fdiv_rn(1.0f, w);
         double prod = 1.0;
-        for (int gd = 0; gd < 3; gd++) {
+        for (int gd = 0; gd < 4; gd++) {
             n[gd] = ext[gd] > 0.f ? (int)floorf(__fmul_rn(ext[gd], inv)) + 1 : 1;
             prod *= (double)n[gd];
         }
@@ -106,13 +109,18 @@ k_grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits,
     if (bad_rs || row_splits[0] != 0 || row_splits[n_rs - 1] != (int64_t)n_vert)
         status |= FGC_STATUS_BAD_ROW_SPLITS;
     const int n_events = n_rs - 1;
-    const int sh = 3 - n_bin_dims;
-    float ext[3];
+    const int G = n_bin_dims >= 4 ? 4 : 3;      // grid dimensions in use
+    const int sh = G - n_bin_dims;
+    float ext[4];
     double vol = 1.0;
     int nz = 0;
     float ext_max = 0.f;
-    for (int gd = 0; gd < 3; gd++) {
-        if (gd < sh || (status & FGC_STATUS_NONFINITE)) {
+    for (int gd = 0; gd < 4; gd++) {
+        if (gd >= G) {
+            g->cdim[gd] = -1;
+            g->origin[gd] = 0.f;
+            ext[gd] = 0.f;
+        } else if (gd < sh || (status & FGC_STATUS_NONFINITE)) {
             g->cdim[gd] = gd < sh ? -1 : gd - sh;
             g->origin[gd] = 0.f;
             ext[gd] = 0.f;
@@ -128,7 +136,7 @@ k_grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits,
         if (ext[gd] > 0.f) { vol *= (double)ext[gd]; nz++; }
         ext_max = fmaxf(ext_max, ext[gd]);
     }
-    int n[3] = {1, 1, 1};
+    int n[4] = {1, 1, 1, 1};
     float w = 1.f;
     if (nz > 0) {
         if (bins_target < 1) bins_target = 1;
@@ -137,19 +145,20 @@ k_grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits,
         if (!(wd > (double)ext_max * 1e-6)) wd = (double)ext_max * 1e-6;
         fit_shape(ext, wd, bins_cap, n, w);
     }
-    long long B = (long long)n[0] * n[1] * n[2];
+    long long B = (long long)n[0] * n[1] * n[2] * n[3];
     if (B > bins_cap) {  // cannot happen after the loop above unless the extents are absurd
-        n[0] = n[1] = n[2] = 1; B = 1; w = fmaxf(ext_max, 1.f) * 2.f;
+        n[0] = n[1] = n[2] = n[3] = 1; B = 1; w = fmaxf(ext_max, 1.f) * 2.f;
         status |= FGC_STATUS_INTERNAL;
     }
-    g->n[0] = n[0]; g->n[1] = n[1]; g->n[2] = n[2];
+    g->n[0] = n[0]; g->n[1] = n[1]; g->n[2] = n[2]; g->n[3] = n[3];
+    g->gdims = G;
     g->B = (int)B;
     g->n_events = n_events;
     g->total_bins = (int)(B * n_events);
     g->w = w;
     g->inv_w = __fdiv_rn(1.0f, w);
     g->slack = 4e-6f * fmaxf(ext_max, w);
-    g->ext[0] = ext[0]; g->ext[1] = ext[1]; g->ext[2] = ext[2];
+    g->ext[0] = ext[0]; g->ext[1] = ext[1]; g->ext[2] = ext[2]; g->ext[3] = ext[3];
     g->bins_cap = bins_cap;
     g->status = status;
 }
@@ -160,44 +169,84 @@ k_grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits,
 // point sees in its own cell; when it is well above the wanted value the grid is rebuilt
 // with cells shrunk by the cube root of the ratio (occupancy scales with the cell volume
 // where the density is locally smooth).
-__device__ void grid_refine(KnnGrid *g, unsigned long long sum_sq, int n_vert, float seen_target)
+// pass 0: the density pass on the first grid.  pass 1: a second one, only after pass 0 fell
+// back from a grid over four coordinates to one over three (D = 4 only): a dense cell table
+// over the four-dimensional bounding box cannot follow strongly clustered data -- the wanted
+// cell size would need far more cells than the table holds -- so data that asks for cells more
+// than 2.8x finer than the mean density suggests is binned in three coordinates, where the
+// same table reaches the wanted size.
+__device__ void grid_refine(KnnGrid *g, unsigned long long sum_sq, int n_vert, float seen_target,
+                            float seen_target3, int bins_target3, int pass, int allow_fallback)
 {
+    const float target = pass == 0 ? seen_target : seen_target3;
     const double seen = (double)sum_sq / (double)(n_vert > 0 ? n_vert : 1);
-    if (!(seen > 1.5 * (double)seen_target)) return;
+    if (!(seen > 1.5 * (double)target)) return;
     int nz = 0;
-    float ext[3], ext_max = 0.f;
-    for (int gd = 0; gd < 3; gd++) {
+    float ext[4], ext_max = 0.f;
+    for (int gd = 0; gd < 4; gd++) {
         ext[gd] = g->ext[gd];
         if (ext[gd] > 0.f) nz++;
         ext_max = fmaxf(ext_max, ext[gd]);
     }
     if (nz == 0) return;
-    double shrink = pow((double)seen_target / seen, 1.0 / (double)nz);
+    double shrink = pow((double)target / seen, 1.0 / (double)nz);
+    int n[4] = {1, 1, 1, 1};
+    float w = g->w;
+    if (pass == 0 && allow_fallback && g->gdims == 4 && shrink < 0.36) {
+        g->gdims = 3;
+        g->cdim[3] = -1; g->origin[3] = 0.f; g->ext[3] = 0.f;
+        ext[3] = 0.f;
+        double vol = 1.0;
+        nz = 0; ext_max = 0.f;
+        for (int gd = 0; gd < 3; gd++) {
+            if (ext[gd] > 0.f) { vol *= (double)ext[gd]; nz++; }
+            ext_max = fmaxf(ext_max, ext[gd]);
+        }
+        if (nz > 0) {
+            double wd = pow(vol / (double)(bins_target3 < 1 ? 1 : bins_target3), 1.0 / (double)nz);
+            if (!(wd > (double)ext_max * 1e-6)) wd = (double)ext_max * 1e-6;
+            fit_shape(ext, wd, g->bins_cap, n, w);
+        } else {
+            w = 1.f;
+        }
+        const long long B3 = (long long)n[0] * n[1] * n[2];
+        g->n[0] = n[0]; g->n[1] = n[1]; g->n[2] = n[2]; g->n[3] = 1;
+        g->B = (int)B3;
+        g->total_bins = (int)(B3 * g->n_events);
+        g->w = w;
+        g->inv_w = __fdiv_rn(1.0f, w);
+        g->slack = 4e-6f * fmaxf(ext_max, w);
+        g->fallback3 = 1;
+        g->refined = 1;
+        g->sum_sq = 0;              // the second density pass starts from scratch
+        g->stat_blocks_done = 0;
+        return;
+    }
     // Never more than 2.2x: data that mixes very dense clusters with a thin background
     // would otherwise pay with long walks through empty cells for the background queries.
     if (shrink < 1.0 / 2.2) shrink = 1.0 / 2.2;
     double wd = (double)g->w * shrink;
     if (!(wd > (double)ext_max * 1e-6)) wd = (double)ext_max * 1e-6;
-    int n[3] = {1, 1, 1};
-    float w = g->w;
     fit_shape(ext, wd, g->bins_cap, n, w);
-    const long long B = (long long)n[0] * n[1] * n[2];
+    const long long B = (long long)n[0] * n[1] * n[2] * n[3];
     if (B > g->bins_cap || !(w < g->w)) return;
-    g->n[0] = n[0]; g->n[1] = n[1]; g->n[2] = n[2];
+    g->n[0] = n[0]; g->n[1] = n[1]; g->n[2] = n[2]; g->n[3] = n[3];
     g->B = (int)B;
     g->total_bins = (int)(B * g->n_events);
     g->w = w;
     g->inv_w = __fdiv_rn(1.0f, w);
     g->slack = 4e-6f * fmaxf(ext_max, w);
-    g->refined = 1;
+    g->refined = pass + 1;
 }
 
 // Every CTA adds its share of sum_c c^2; the CTA that finishes last (a ticket counter, no
 // waiting) decides about the finer grid.
 __global__ void __launch_bounds__(256)
-k_cell_stat_refine(const int *__restrict__ counts, KnnGrid *g, int n_vert, float seen_target)
+k_cell_stat_refine(const int *__restrict__ counts, KnnGrid *g, int n_vert, float seen_target,
+                   float seen_target3, int bins_target3, int pass, int allow_fallback)
 {
     if (g->status != 0) return;
+    if (pass == 1 && !g->fallback3) return;
     const int n = g->total_bins;
     unsigned long long s = 0;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -213,15 +262,16 @@ k_cell_stat_refine(const int *__restrict__ counts, KnnGrid *g, int n_vert, float
         const int ticket = atomicAdd(&g->stat_blocks_done, 1);
         if (ticket == (int)gridDim.x - 1) {
             __threadfence();
-            grid_refine(g, atomicAdd(&g->sum_sq, 0ull), n_vert, seen_target);
+            grid_refine(g, atomicAdd(&g->sum_sq, 0ull), n_vert, seen_target, seen_target3, bins_target3, pass,
+                        allow_fallback);
         }
     }
 }
 
 __global__ void __launch_bounds__(256)
-k_zero_counts(int *__restrict__ counts, const KnnGrid *g, int only_if_refined)
+k_zero_counts(int *__restrict__ counts, const KnnGrid *g, int stage)
 {
-    if (only_if_refined && !g->refined) return;
+    if (g->refined < stage) return;      // stage s follows the s-th density pass that changed the grid
     const int n = g->total_bins + 1;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
         counts[i] = 0;
@@ -240,22 +290,23 @@ __global__ void __launch_bounds__(256)
 k_histogram(const float *__restrict__ coords, int n_vert, int n_coords,
             const int64_t *__restrict__ row_splits, int n_rs, const KnnGrid *__restrict__ g,
             int *__restrict__ counts, int *__restrict__ pbin, int *__restrict__ prank,
-            int only_if_refined)
+            int stage)
 {
-    if (only_if_refined && !g->refined) return;
+    if (g->refined < stage) return;
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     const bool live = v < n_vert && g->status == 0;
     int flat = 0;
     if (live) {
         const float *row = coords + (size_t)v * n_coords;
-        int b[3];
+        int b[4];
 #pragma unroll
-        for (int gd = 0; gd < 3; gd++) {
+        for (int gd = 0; gd < 4; gd++) {
             const int c = g->cdim[gd];
             b[gd] = c < 0 ? 0 : cell_of(__ldg(row + c), g->origin[gd], g->inv_w, g->n[gd]);
         }
         const int e = row_split_of(row_splits, n_rs, v);
-        flat = e * g->B + (b[0] * g->n[1] + b[1]) * g->n[2] + b[2];
+        // the fourth dimension has one cell (b[3] = 0) in a grid over three coordinates
+        flat = e * g->B + ((b[0] * g->n[1] + b[1]) * g->n[2] + b[2]) * g->n[3] + b[3];
     }
     const unsigned active = __ballot_sync(FGC_FULL_MASK, live);
     if (live) {
@@ -475,7 +526,7 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
 
     const int n = (int)n_vert;
     const int n_events = (int)n_rs - 1;
-    const int n_bin_dims = n_coords < 3 ? n_coords : 3;
+    const int n_bin_dims = n_coords < 4 ? n_coords : 4;
     // target_occupancy > 0: one fixed grid with that mean occupancy.  Otherwise: mean
     // occupancy 2, then the density pass may shrink the cells so that a typical point sees
     // about seen_target points in its own cell.
@@ -483,7 +534,8 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
     if (adaptive) target_occupancy = 2.0f;
     float seen_target = (float)K / 6.0f;
     if (seen_target < 4.f) seen_target = 4.f;
-    if (n_coords > 3) seen_target *= 2.f;   // coordinates beyond the binned three thin the cells out
+    const float seen_target3 = seen_target * 2.f;    // D = 4 binned in three coordinates
+    if (n_coords > n_bin_dims) seen_target *= 2.f;   // coordinates that are not binned thin the cells out
     const int64_t bins_cap64 = L.cap_bins / n_events;
     const int bins_cap = (int)(bins_cap64 < 1 ? 1 : bins_cap64);
     const double bt = (double)n_vert / (double)n_events / (double)target_occupancy;
@@ -506,13 +558,25 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
                                           pbin, prank, 0);
     FGC_CHECK_LAUNCH();
     if (adaptive) {
-        k_cell_stat_refine<<<148 * 4, 256, 0, s>>>(counts, grid, n, seen_target);
+        const int allow_fallback = n_coords == 4;
+        k_cell_stat_refine<<<148 * 4, 256, 0, s>>>(counts, grid, n, seen_target, seen_target3, bins_target, 0,
+                                                    allow_fallback);
         FGC_CHECK_LAUNCH();
         k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid, 1);
         FGC_CHECK_LAUNCH();
         k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
                                               pbin, prank, 1);
         FGC_CHECK_LAUNCH();
+        if (allow_fallback) {
+            // second density pass: runs only when the first one fell back to three coordinates
+            k_cell_stat_refine<<<148 * 4, 256, 0, s>>>(counts, grid, n, seen_target, seen_target3, bins_target, 1, 0);
+            FGC_CHECK_LAUNCH();
+            k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid, 2);
+            FGC_CHECK_LAUNCH();
+            k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
+                                                  pbin, prank, 2);
+            FGC_CHECK_LAUNCH();
+        }
     }
     k_scan_tile_sums<<<scan_blocks, 256, 0, s>>>(counts, &grid->total_bins, 1, blocksums);
     FGC_CHECK_LAUNCH();
@@ -552,7 +616,7 @@ extern "C" int fgc_knn_read_counters(const void *workspace, uint64_t *counters_h
     FGC_RETURN_IF_CUDA(cudaMemcpyAsync(&h, workspace, sizeof(KnnGrid), cudaMemcpyDeviceToHost, s));
     FGC_RETURN_IF_CUDA(cudaStreamSynchronize(s));
     if (counters_host) for (int i = 0; i < 8; i++) counters_host[i] = h.counters[i];
-    if (grid_shape_host) { grid_shape_host[0] = h.n[0]; grid_shape_host[1] = h.n[1]; grid_shape_host[2] = h.n[2]; }
+    if (grid_shape_host) { grid_shape_host[0] = h.n[0]; grid_shape_host[1] = h.n[1]; grid_shape_host[2] = h.n[2] * h.n[3]; }
     if (cell_width_host) *cell_width_host = h.w;
     return FGC_OK;
 }

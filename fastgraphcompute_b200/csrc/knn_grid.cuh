@@ -12,28 +12,33 @@
 
 namespace fgc {
 
-// Grid over up to three coordinate dimensions.  Grid dimension g uses
-// coordinate dimension cdim[g]; unused leading grid dimensions have n = 1.
-// Cell (e, b0, b1, b2) of row split e has flat id e*B + (b0*n[1] + b1)*n[2] + b2,
-// so the cells of one (e, b0, b1) line are consecutive and, after the counting
-// sort, so are their points.
+// Grid over the first min(D, 4) coordinate dimensions.  With D <= 3 the grid has three
+// dimensions (gdims = 3): grid dimension g uses coordinate dimension cdim[g], unused leading
+// grid dimensions have n = 1, and cell (e, b0, b1, b2) of row split e has flat id
+// e*B + (b0*n[1] + b1)*n[2] + b2.  With D >= 4 it has four (gdims = 4, cdim[g] = g) and the
+// flat id is e*B + ((b0*n[1] + b1)*n[2] + b2)*n[3] + b3.  Either way the cells of one line
+// along the last grid dimension are consecutive and, after the counting sort, so are
+// their points.
 struct KnnGrid {
     int32_t status;        // FGC_STATUS_* bits (first word of the workspace)
     int32_t n_events;
-    int32_t n[3];          // cells per grid dimension
-    int32_t cdim[3];       // coordinate dimension of grid dimension g, -1 = unused
+    int32_t n[4];          // cells per grid dimension (1 for an unused one)
+    int32_t cdim[4];       // coordinate dimension of grid dimension g, -1 = unused
+    int32_t gdims;         // 3 or 4
     int32_t B;             // cells per row split = n[0]*n[1]*n[2]
     int32_t total_bins;    // n_events * B
-    float origin[3];       // global minimum of the coordinate
+    float origin[4];       // global minimum of the coordinate
     float w;               // cell width
     float inv_w;           // 1 / w
     float slack;           // absolute safety margin for cell-distance bounds
-    uint32_t min_key[3];   // ~ordered(min) per binned coordinate (atomicMax)
-    uint32_t max_key[3];   // ordered(max)
+    uint32_t min_key[4];   // ~ordered(min) per binned coordinate (atomicMax)
+    uint32_t max_key[4];   // ordered(max)
     uint32_t nonfinite;    // set when any coordinate is NaN/Inf
-    float ext[3];          // extent of the bounding box per grid dimension
+    float ext[4];          // extent of the bounding box per grid dimension
     int32_t bins_cap;      // largest cell count per row split the table can hold
-    int32_t refined;       // 1 when the density pass replaced the first grid by a finer one
+    int32_t refined;       // number of density passes that replaced the grid (0, 1 or 2)
+    int32_t fallback3;     // 1: D = 4 data too clustered for a table over four coordinates,
+                           // the grid was rebuilt over the first three
     int32_t n_big_cells;   // length of the work list of cells sorted by one warp each
     int32_t n_huge_cells;  // length of the work list of cells sorted by one CTA each
     int32_t stat_blocks_done;   // CTAs of the density pass that have added their share
@@ -80,6 +85,32 @@ __host__ __device__ inline void shell_item_decode(int d, int u, int &o0, int &o1
         o1 = t - tq * half - (d - 1);
         zlo = zhi = (c & 1) ? d : -d;
     }
+}
+
+// Grids over four coordinates: shell d = the lines whose three leading offsets have Chebyshev
+// norm d, each with its whole run of 2d+1 cells, plus the two end cells of every interior line.
+// Shells up to kShellTable4MaxD come from a table (nearest first, exact item count); beyond
+// that every offset triple of the (2d+1)^3 cube yields two items, the second one of a rim line
+// being empty.
+constexpr int kShellTable4MaxD = 2;
+__host__ __device__ inline int shell_items4(int d)
+{
+    if (d == 0) return 1;
+    const int a = 2 * d + 1, b = 2 * d - 1;
+    return d <= kShellTable4MaxD ? a * a * a + b * b * b : 2 * a * a * a;
+}
+__host__ __device__ inline int shell_table4_offset(int d) { return d == 0 ? 0 : (d == 1 ? 1 : 29); }
+__host__ __device__ inline void shell_item_decode4(int d, int u, int &o0, int &o1, int &o2, int &zlo, int &zhi)
+{
+    const int side = 2 * d + 1;
+    const int t = u >> 1, which = u & 1;
+    o0 = t / (side * side) - d;
+    o1 = (t / side) % side - d;
+    o2 = t % side - d;
+    const int a0 = o0 < 0 ? -o0 : o0, a1 = o1 < 0 ? -o1 : o1, a2 = o2 < 0 ? -o2 : o2;
+    const bool rim = a0 == d || a1 == d || a2 == d;
+    if (rim) { zlo = which ? 1 : -d; zhi = which ? 0 : d; }     // second item of a rim line: empty
+    else { zlo = zhi = which ? d : -d; }
 }
 
 // Cells of up to kRankMax points are put in order by ranking (every point counts the smaller

@@ -12,6 +12,10 @@
 // K-1 best live in registers, spread over the lanes.  The search of a query ends as soon
 // as the cube of cells it has covered contains the ball of its K-th distance.
 //
+// The grid spans the first three coordinates (D <= 3: items are (o0, o1, run)) or the first
+// four (D >= 4: items are (o0, o1, o2, run)); for D = 4 the grid build picks one of the two on
+// the device (knn_grid.cu: strongly clustered data goes to three) and the kernel branches once.
+//
 // What is computed is what the reference's CPU path computes
 // (extensions/binned_knn_autograd_kernel.cpp:85-209 with
 // extensions/binned_select_knn_cpu.cpp:56-208): per row split, the K-1 nearest other
@@ -133,9 +137,9 @@ struct NeighbourList {
     }
 };
 
-template <int NV, int R, bool COUNT>
-__global__ void __launch_bounds__(kKnnWarps * 32, (R == 1 ? 8 : (R == 2 ? 7 : (R == 4 ? 6 : 4))))
-k_knn(const KnnArgs a)
+// The search of one query by one warp.  G4: the grid spans four coordinates, else three.
+template <int NV, int R, bool COUNT, bool G4>
+__device__ __forceinline__ void knn_query(const KnnArgs &a)
 {
     __shared__ int s_delta[kKnnWarps][32];
     __shared__ float s_bd[kKnnWarps][32];
@@ -224,14 +228,19 @@ k_knn(const KnnArgs a)
     };
 
     if (!q_inactive && kn > 0) {
-        const int B = g->B, n0 = g->n[0], n1 = g->n[1], n2 = g->n[2];
+        const int B = g->B, n0 = g->n[0], n1 = g->n[1], n2 = g->n[2], n3 = G4 ? g->n[3] : 1;
         const int flat = __ldg(a.sbin + qi);
         const int e = flat / B;
         int rem = flat - e * B;
-        const int b0 = rem / (n1 * n2);
-        rem -= b0 * n1 * n2;
-        const int b1 = rem / n2;
-        const int b2 = rem - b1 * n2;
+        const int b0 = rem / (n1 * n2 * n3);
+        rem -= b0 * n1 * n2 * n3;
+        const int b1 = rem / (n2 * n3);
+        rem -= b1 * n2 * n3;
+        const int b2 = G4 ? rem / n3 : rem;
+        const int b3 = G4 ? rem - b2 * n3 : 0;
+        // the run of an item lies along the last grid dimension
+        const int bl = G4 ? b3 : b2, nl = G4 ? n3 : n2;
+        constexpr int GD = G4 ? 4 : 3;
         const int ev_begin = __ldg(a.bounds + e * B);
         const int ev_end = __ldg(a.bounds + (e + 1) * B);
         const int n_e = ev_end - ev_begin;
@@ -241,13 +250,13 @@ k_knn(const KnnArgs a)
             const float w = g->w, slack = g->slack;
             const float w_lo = w * (1.0f - 1e-6f), w_hi = w * (1.0f + 1e-6f);
             // query position relative to the grid origin, per grid dimension
-            float qr[3];
+            float qr[GD];
             {
-                const float qc[3] = {q[0].x, q[0].y, q[0].z};
+                const float qc[4] = {q[0].x, q[0].y, q[0].z, q[0].w};
 #pragma unroll
-                for (int gd = 0; gd < 3; gd++) {
+                for (int gd = 0; gd < GD; gd++) {
                     const int c = g->cdim[gd];
-                    const float x = c == 0 ? qc[0] : (c == 1 ? qc[1] : qc[2]);
+                    const float x = c == 0 ? qc[0] : (c == 1 ? qc[1] : (c == 2 ? qc[2] : qc[3]));
                     qr[gd] = c < 0 ? 0.f : __fsub_rn(x, g->origin[gd]);
                 }
             }
@@ -270,39 +279,55 @@ k_knn(const KnnArgs a)
             const bool merged = __ldg(a.bounds + flat + 1) - __ldg(a.bounds + flat) < 2 * K;
             for (int d = merged ? 1 : 0;; ++d) {
                 const bool first = merged && d == 1;
-                const int n_items = first ? 1 + shell_items(1) : shell_items(d);
-                const int32_t *tab = first ? kShellTableData
-                                   : (d <= kShellTableMaxD ? kShellTableData + shell_table_offset(d) : nullptr);
+                const int n_items = G4 ? (first ? 1 + shell_items4(1) : shell_items4(d))
+                                       : (first ? 1 + shell_items(1) : shell_items(d));
+                const int32_t *tab =
+                    G4 ? (first ? kShellTable4Data
+                                : (d <= kShellTable4MaxD ? kShellTable4Data + shell_table4_offset(d) : nullptr))
+                       : (first ? kShellTableData
+                                : (d <= kShellTableMaxD ? kShellTableData + shell_table_offset(d) : nullptr));
                 for (int base = 0; base < n_items; base += 32) {
                     const int u = base + lane;
                     bool valid = u < n_items;
-                    int o0 = 0, o1 = 0, zlo = 0, zhi = 0;
+                    int o0 = 0, o1 = 0, o2 = 0, zlo = 0, zhi = 0;
                     if (valid) {
                         if (tab) {
                             const int32_t t = __ldg(tab + u);
-                            o0 = (int)(int8_t)(t & 0xff);
-                            o1 = (int)(int8_t)((t >> 8) & 0xff);
-                            zlo = (int)(int8_t)((t >> 16) & 0xff);
-                            zhi = (int)(int8_t)((t >> 24) & 0xff);
+                            if (G4) {
+                                o0 = (t & 0xf) - 8;
+                                o1 = ((t >> 4) & 0xf) - 8;
+                                o2 = ((t >> 8) & 0xf) - 8;
+                                zlo = ((t >> 12) & 0xf) - 8;
+                                zhi = ((t >> 16) & 0xf) - 8;
+                            } else {
+                                o0 = (int)(int8_t)(t & 0xff);
+                                o1 = (int)(int8_t)((t >> 8) & 0xff);
+                                zlo = (int)(int8_t)((t >> 16) & 0xff);
+                                zhi = (int)(int8_t)((t >> 24) & 0xff);
+                            }
+                        } else if (G4) {
+                            shell_item_decode4(d, u, o0, o1, o2, zlo, zhi);
                         } else {
                             shell_item_decode(d, u, o0, o1, zlo, zhi);
                         }
                     }
-                    const int g0 = b0 + o0, g1 = b1 + o1;
+                    const int g0 = b0 + o0, g1 = b1 + o1, g2 = b2 + o2;
                     valid = valid && g0 >= 0 && g0 < n0 && g1 >= 0 && g1 < n1;
-                    zlo = max(b2 + zlo, 0);
-                    zhi = min(b2 + zhi, n2 - 1);
+                    if (G4) valid = valid && g2 >= 0 && g2 < n2 && zlo <= zhi;
+                    zlo = max(bl + zlo, 0);
+                    zhi = min(bl + zhi, nl - 1);
                     valid = valid && zlo <= zhi;
                     if (valid && list.tau < kInfBits) {
                         const float ga = gap_to(g0, g0, b0, qr[0]);
                         const float gb = gap_to(g1, g1, b1, qr[1]);
-                        const float gc = gap_to(zlo, zhi, b2, qr[2]);
-                        const float md = ga * ga + gb * gb + gc * gc;
+                        const float gc = gap_to(zlo, zhi, bl, qr[GD - 1]);
+                        float md = ga * ga + gb * gb + gc * gc;
+                        if (G4) { const float gm = gap_to(g2, g2, b2, qr[2]); md += gm * gm; }
                         if (md > __uint_as_float(list.tau) * 1.00001f) valid = false;
                     }
                     int start = 0, len = 0;
                     if (valid) {
-                        const int rowbase = e * B + (g0 * n1 + g1) * n2;
+                        const int rowbase = G4 ? e * B + ((g0 * n1 + g1) * n2 + g2) * n3 : e * B + (g0 * n1 + g1) * n2;
                         start = __ldg(a.bounds + rowbase + zlo);
                         len = __ldg(a.bounds + rowbase + zhi + 1) - start;
                     }
@@ -341,10 +366,10 @@ k_knn(const KnnArgs a)
                 float fd = __uint_as_float(kInfBits);
                 bool any = false;
                 {
-                    const int bq[3] = {b0, b1, b2};
-                    const int nn[3] = {n0, n1, n2};
+                    const int bq[4] = {b0, b1, b2, b3};
+                    const int nn[4] = {n0, n1, n2, n3};
 #pragma unroll
-                    for (int gd = 0; gd < 3; gd++) {
+                    for (int gd = 0; gd < GD; gd++) {
                         const int hi = bq[gd] + d + 1, lo = bq[gd] - d - 1;
                         if (hi <= nn[gd] - 1) { fd = fminf(fd, fmaxf((float)hi * w_lo - qr[gd] - slack, 0.f)); any = true; }
                         if (lo >= 0) { fd = fminf(fd, fmaxf(qr[gd] - (float)(lo + 1) * w_hi - slack, 0.f)); any = true; }
@@ -405,7 +430,20 @@ k_knn(const KnnArgs a)
     }
 }
 
-template <int NV>
+// MODE 0: grid over three coordinates (D <= 3); 1: over four (D >= 5); 2: D = 4, where the grid
+// build decides on the device between the two -- one launch, one uniform branch (two launches
+// of which one returns at once cost the same; out-of-line bodies were slower).
+template <int NV, int R, bool COUNT, int MODE>
+__global__ void __launch_bounds__(kKnnWarps * 32, (R == 1 ? 8 : (R == 2 ? 7 : (R == 4 ? 6 : 4))))
+k_knn(const KnnArgs a)
+{
+    if (MODE == 0) knn_query<NV, R, COUNT, false>(a);
+    else if (MODE == 1) knn_query<NV, R, COUNT, true>(a);
+    else if (a.grid->gdims == 4) knn_query<NV, R, COUNT, true>(a);
+    else knn_query<NV, R, COUNT, false>(a);
+}
+
+template <int NV, int G4>
 static int launch_knn_nv(const KnnArgs &a, cudaStream_t s)
 {
     const int kn = a.K - 1;
@@ -413,23 +451,18 @@ static int launch_knn_nv(const KnnArgs &a, cudaStream_t s)
     const int R = (kn + 31) / 32;
     const int T = kKnnWarps * 32;
     if (a.count_evals) {
-        if (R <= 1) k_knn<NV, 1, true><<<blocks, T, 0, s>>>(a);
-        else if (R <= 2) k_knn<NV, 2, true><<<blocks, T, 0, s>>>(a);
-        else if (R <= 4) k_knn<NV, 4, true><<<blocks, T, 0, s>>>(a);
-        else k_knn<NV, 8, true><<<blocks, T, 0, s>>>(a);
+        if (R <= 1) k_knn<NV, 1, true, G4><<<blocks, T, 0, s>>>(a);
+        else if (R <= 2) k_knn<NV, 2, true, G4><<<blocks, T, 0, s>>>(a);
+        else if (R <= 4) k_knn<NV, 4, true, G4><<<blocks, T, 0, s>>>(a);
+        else k_knn<NV, 8, true, G4><<<blocks, T, 0, s>>>(a);
     } else {
-        if (R <= 1) k_knn<NV, 1, false><<<blocks, T, 0, s>>>(a);
-        else if (R <= 2) k_knn<NV, 2, false><<<blocks, T, 0, s>>>(a);
-        else if (R <= 4) k_knn<NV, 4, false><<<blocks, T, 0, s>>>(a);
-        else k_knn<NV, 8, false><<<blocks, T, 0, s>>>(a);
+        if (R <= 1) k_knn<NV, 1, false, G4><<<blocks, T, 0, s>>>(a);
+        else if (R <= 2) k_knn<NV, 2, false, G4><<<blocks, T, 0, s>>>(a);
+        else if (R <= 4) k_knn<NV, 4, false, G4><<<blocks, T, 0, s>>>(a);
+        else k_knn<NV, 8, false, G4><<<blocks, T, 0, s>>>(a);
     }
     return (int)cudaGetLastError();
 }
-
-}  // namespace fgc
-
-namespace fgc {
-
 template <int NV>
 static int launch_tiles(const KnnTileArgs &t, bool count, cudaStream_t s)
 {
@@ -462,7 +495,8 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     cudaStream_t s = (cudaStream_t)stream;
     char *ws = (char *)workspace;
     const bool count = (flags & FGC_SEARCH_COUNT) != 0;
-    const bool use_tiles = (flags & FGC_SEARCH_TILES) && K >= 2 && K - 1 <= kTileMaxNeighbours && L.nv <= 2;
+    // the tile pass knows grids over three coordinates only
+    const bool use_tiles = (flags & FGC_SEARCH_TILES) && K >= 2 && K - 1 <= kTileMaxNeighbours && n_coords <= 3;
     KnnArgs a;
     a.scoords = (const float4 *)(ws + L.scoords);
     a.sorig = (const int *)(ws + L.sorig);
@@ -491,10 +525,11 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
         if (trc != 0) return trc;
         if (flags & 4) return FGC_OK;   // timing aid: tile pass alone (rows of other queries stay unwritten)
     }
-    if (L.nv == 1) return launch_knn_nv<1>(a, s);
-    if (L.nv == 2) return launch_knn_nv<2>(a, s);
-    if (L.nv == 3) return launch_knn_nv<3>(a, s);
-    return launch_knn_nv<4>(a, s);
+    if (n_coords <= 3) return launch_knn_nv<1, 0>(a, s);
+    if (L.nv == 1) return launch_knn_nv<1, 2>(a, s);
+    if (L.nv == 2) return launch_knn_nv<2, 1>(a, s);
+    if (L.nv == 3) return launch_knn_nv<3, 1>(a, s);
+    return launch_knn_nv<4, 1>(a, s);
 }
 
 extern "C" int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,
