@@ -83,6 +83,9 @@ SIGNATURES = {
                                           c_void_p]),
     "fgc_knn_build_grid": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_void_p, c_i64, c_i32, c_void_p,
                                           c_float, c_void_p, c_size, c_void_p]),
+    "fgc_knn_build_grid_dims": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_void_p, c_i64, c_i32, c_void_p,
+                                               c_float, c_i32, c_void_p, c_size, c_void_p]),
+    "fgc_knn_publish_grid_info": (ctypes.c_int, [c_void_p, c_void_p, c_void_p]),
     "fgc_knn_search": (ctypes.c_int, [c_i64, c_i32, c_i64, c_i32, c_i32, c_i32, c_i32, c_void_p,
                                       c_void_p, c_void_p, c_size, c_void_p]),
     "fgc_knn_read_counters": (ctypes.c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint64),

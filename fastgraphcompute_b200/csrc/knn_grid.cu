@@ -458,6 +458,16 @@ k_sort_large_cells(const float *__restrict__ coords, int n_coords, int nv,
     }
 }
 
+// Status word and the grid's form ((3 or 4) + 16 * fallback3) to memory the host can read.
+__global__ void k_publish_grid_info(const KnnGrid *__restrict__ g, volatile int32_t *info_mapped)
+{
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        info_mapped[0] = g->status;
+        info_mapped[1] = g->gdims + 16 * g->fallback3;
+        __threadfence_system();
+    }
+}
+
 // One store of the status word to memory the host can read (mapped pinned memory).
 __global__ void k_publish_status(const int32_t *__restrict__ status_dev, volatile int32_t *status_mapped)
 {
@@ -495,12 +505,31 @@ extern "C" int fgc_publish_status(const void *workspace_or_params, int32_t *stat
     return FGC_OK;
 }
 
+extern "C" int fgc_knn_publish_grid_info(const void *workspace, int32_t *info_mapped, fgc_stream_t stream)
+{
+    if (!workspace || !info_mapped) return FGC_ERR_BAD_ARGUMENT;
+    fgc::k_publish_grid_info<<<1, 32, 0, (cudaStream_t)stream>>>((const fgc::KnnGrid *)workspace, info_mapped);
+    FGC_CHECK_LAUNCH();
+    return FGC_OK;
+}
+
 extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n_coords,
                                   const int64_t *row_splits, int64_t n_rs, int32_t K,
                                   const int64_t *direction_or_null, float target_occupancy,
                                   void *workspace, size_t workspace_bytes, fgc_stream_t stream)
 {
+    return fgc_knn_build_grid_dims(coords, n_vert, n_coords, row_splits, n_rs, K, direction_or_null,
+                                   target_occupancy, 0, workspace, workspace_bytes, stream);
+}
+
+extern "C" int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int32_t n_coords,
+                                       const int64_t *row_splits, int64_t n_rs, int32_t K,
+                                       const int64_t *direction_or_null, float target_occupancy,
+                                       int32_t grid_dims, void *workspace, size_t workspace_bytes,
+                                       fgc_stream_t stream)
+{
     using namespace fgc;
+    if (grid_dims != 0 && grid_dims != 3 && grid_dims != 4) return FGC_ERR_BAD_ARGUMENT;
     KnnWorkspace L;
     if (!row_splits) return FGC_ERR_BAD_ARGUMENT;
     const int rc = check_knn_args(n_vert, n_coords, n_rs, K, workspace, workspace_bytes, &L);
@@ -526,7 +555,10 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
 
     const int n = (int)n_vert;
     const int n_events = (int)n_rs - 1;
-    const int n_bin_dims = n_coords < 4 ? n_coords : 4;
+    // D = 4 lets the density pass choose between four and three binned coordinates unless the
+    // caller fixes the choice (grid_dims 3 or 4; ignored for every other D)
+    const int forced = n_coords == 4 ? grid_dims : 0;
+    const int n_bin_dims = forced == 3 ? 3 : (n_coords < 4 ? n_coords : 4);
     // target_occupancy > 0: one fixed grid with that mean occupancy.  Otherwise: mean
     // occupancy 2, then the density pass may shrink the cells so that a typical point sees
     // about seen_target points in its own cell.
@@ -558,7 +590,7 @@ extern "C" int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n
                                           pbin, prank, 0);
     FGC_CHECK_LAUNCH();
     if (adaptive) {
-        const int allow_fallback = n_coords == 4;
+        const int allow_fallback = n_coords == 4 && forced == 0;
         k_cell_stat_refine<<<148 * 4, 256, 0, s>>>(counts, grid, n, seen_target, seen_target3, bins_target, 0,
                                                     allow_fallback);
         FGC_CHECK_LAUNCH();

@@ -149,6 +149,10 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
     const int qi = blockIdx.x * kKnnWarps + wib;   // position in cell order
     KnnGrid *__restrict__ g = a.grid;
     if (qi >= a.n_vert || g->status != 0) return;
+    if ((g->gdims == 4) != G4) {            // built in the other form: never walk it
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(&g->status, FGC_STATUS_INTERNAL);
+        return;
+    }
     if (a.done && a.done[qi]) return;
 
     const int K = a.K, kn = K - 1;
@@ -526,7 +530,13 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
         if (flags & 4) return FGC_OK;   // timing aid: tile pass alone (rows of other queries stay unwritten)
     }
     if (n_coords <= 3) return launch_knn_nv<1, 0>(a, s);
-    if (L.nv == 1) return launch_knn_nv<1, 2>(a, s);
+    if (L.nv == 1) {
+        // D = 4: a caller that fixed the grid's form at build time says so here too and gets the
+        // kernel with that one search only (it checks the grid record and refuses a mismatch)
+        if (flags & FGC_SEARCH_GRID3) return launch_knn_nv<1, 0>(a, s);
+        if (flags & FGC_SEARCH_GRID4) return launch_knn_nv<1, 1>(a, s);
+        return launch_knn_nv<1, 2>(a, s);
+    }
     if (L.nv == 2) return launch_knn_nv<2, 1>(a, s);
     if (L.nv == 3) return launch_knn_nv<3, 1>(a, s);
     return launch_knn_nv<4, 1>(a, s);

@@ -162,8 +162,26 @@ int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n_coords,
                        const int64_t *row_splits, int64_t n_rs, int32_t K,
                        const int64_t *direction_or_null, float target_occupancy,
                        void *workspace, size_t workspace_bytes, fgc_stream_t stream);
+/*
+ * D = 4 only: the grid spans four coordinates unless the data is strongly clustered, in which
+ * case the density pass rebuilds it over three (decided on the device).  A caller that knows
+ * its data fixes the form: fgc_knn_build_grid_dims(..., grid_dims = 3 or 4, ...) and the
+ * matching FGC_SEARCH_GRID3 / FGC_SEARCH_GRID4 flag for fgc_knn_search, which saves the trial
+ * histogram and runs a kernel that holds one search only.  grid_dims = 0 and no flag: automatic.
+ * fgc_knn_publish_grid_info stores {status word, (3 or 4) + 16 * fell_back} into mapped pinned
+ * memory (like fgc_publish_status) so that a host can learn the choice without a copy.
+ * No counterparts in the reference.
+ */
+int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int32_t n_coords,
+                            const int64_t *row_splits, int64_t n_rs, int32_t K,
+                            const int64_t *direction_or_null, float target_occupancy,
+                            int32_t grid_dims, void *workspace, size_t workspace_bytes,
+                            fgc_stream_t stream);
+int fgc_knn_publish_grid_info(const void *workspace, int32_t *info_mapped, fgc_stream_t stream);
 #define FGC_SEARCH_COUNT 1     /* flags: accumulate the debug counters */
 #define FGC_SEARCH_TILES 2     /* flags: run the tile pass before the warp-per-query pass */
+#define FGC_SEARCH_GRID3 8     /* flags: the grid was built with grid_dims = 3 (D = 4) */
+#define FGC_SEARCH_GRID4 16    /* flags: the grid was built with grid_dims = 4 (D = 4) */
 int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
                    int32_t has_direction, int32_t tf_compat, int32_t flags,
                    int64_t *out_idx, float *out_distsq, void *workspace,
