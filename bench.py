@@ -34,11 +34,11 @@ UNIT = "points/s"
 WORKLOAD = "c2: single-event binned kNN fwd+bwd, N=200000, D=4, K=32, 50-component Gaussian mixture sigma=0.02"
 L2_FLUSH_BYTES = 256 << 20
 
-# DRAM traffic of one k_knn launch on this workload: dram__bytes_read.sum (8.56 MB) +
-# dram__bytes_write.sum (58.56 MB) of the ncu capture summarised in
+# DRAM traffic of one k_knn launch on this workload: dram__bytes_read.sum (8.54 MB) +
+# dram__bytes_write.sum (53.18 MB) of the ncu capture summarised in
 # profiles/k_knn_c2_ncu_full.md.  Below the 80 MB of algorithmic bytes because part of the
 # output is still in the 126 MB L2 when the kernel ends.
-KNN_KERNEL_DRAM_TRAFFIC_BYTES = 67116800
+KNN_KERNEL_DRAM_TRAFFIC_BYTES = 61718272
 
 
 def env_int(name, default):
@@ -731,7 +731,7 @@ def run_b200(args):
         d = w.coords.shape[1]
         alg_bytes = n * (4 * d + 8 * K + 4 * K)          # coords read + int64 idx + fp32 distsq written
         achieved = alg_bytes / (knn_ms_avg * 1e-3) / 1e9
-        launches_per_step = (_cabi.KERNELS_BUILD_GRID_D4 + _cabi.KERNELS_PUBLISH_STATUS + _cabi.KERNELS_SEARCH +
+        launches_per_step = (_cabi.KERNELS_BUILD_GRID + _cabi.KERNELS_PUBLISH_STATUS + _cabi.KERNELS_SEARCH +
                              _cabi.KERNELS_KNN_BWD)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -752,7 +752,7 @@ def run_b200(args):
                          "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": "of " + peak_kind, "traffic": KNN_KERNEL_DRAM_TRAFFIC_BYTES,
                          "algorithmic_bytes_per_launch": alg_bytes, "kernel_ms": knn_ms_avg,
-                         "note": "not HBM-bound: ncu shows 88 % of issue slots busy, DRAM at 1.0 % "
+                         "note": "not HBM-bound: ncu shows 85 % of issue slots busy, DRAM at 0.9 % "
                                  "(profiles/k_knn_c2_ncu_full.md)"},
             "roofline_fp32": {"note": "the search is bound by CUDA-core issue, not by HBM: distance evaluations x 3*D flops",
                               "distance_evals_per_launch": n_evals, "evals_per_query": n_evals / n,
