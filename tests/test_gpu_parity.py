@@ -6,6 +6,7 @@ Bars: bin indices / histograms / index_replacer bit-exact; kNN index sets exact 
 ties with squared distances within 1e-6 relative (tests/parity.py); gradients within 1e-5 of
 the gradient's scale.
 """
+import ctypes
 import os
 
 import numpy as np
@@ -239,6 +240,54 @@ def test_knn_forward_backward_in_a_cuda_graph():
             parity.assert_grad_close(grad_g.cpu().numpy(), ref.grad.cpu().numpy(), what="graph replay grad")
     finally:
         km.check_status = True
+
+
+def test_knn_four_coordinates_grid_forms_agree():
+    """D = 4: the grid over four coordinates, the one over three, the device's own choice and the
+    wrapper's memory of that choice all give the oracle's neighbour sets; a search told the wrong
+    form refuses to walk the grid and raises the internal status bit."""
+    import importlib
+    from fastgraphcompute_b200 import _cabi
+    km = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
+    g = torch.Generator().manual_seed(12)
+    blob = torch.randn((3000, 4), generator=g)                                     # fills its bounding box
+    centres = torch.rand((20, 4), generator=g)
+    clustered = centres[torch.randint(0, 20, (3000,), generator=g)] + 0.002 * torch.randn((3000, 4), generator=g)
+    rs = torch.tensor([0, 1300, 3000], dtype=torch.int64)
+    old = km.grid_dims
+    try:
+        for name, pts in (("blob", blob), ("clustered", clustered)):
+            oi, od = oracle.binned_select_knn(20, pts.numpy(), rs.numpy())
+            chosen = {}
+            for mode in (-1, 3, 4, 0, 0):
+                km.grid_dims = mode
+                km._grid_memory.clear() if mode != 0 else None
+                idx, dist, ws = km.knn_forward_raw(pts.to(DEV), rs.to(DEV), 20, None, False)
+                parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), oi, od, what="%s grid_dims=%d" % (name, mode))
+                info = torch.empty(2, dtype=torch.int32).pin_memory()
+                assert _cabi.lib.fgc_knn_publish_grid_info(_cabi.ptr(ws), info.data_ptr(), _cabi.current_stream(ws.device)) == 0
+                torch.cuda.synchronize()
+                chosen[mode] = int(info[1]) & 15
+            assert chosen[3] == 3 and chosen[4] == 4 and chosen[0] == chosen[-1]
+            assert km._grid_memory[(0, 3000, 3, 20)][0] == chosen[-1]     # remembered after the first automatic call
+        # wrong form at search time: nothing is walked, the status word says so
+        pts, n = blob.to(DEV), 3000
+        nbytes = _cabi.lib.fgc_knn_workspace_bytes(n, 4, 3, 20)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+        st = _cabi.current_stream(ws.device)
+        rsd = rs.to(DEV)
+        assert _cabi.lib.fgc_knn_build_grid_dims(_cabi.ptr(pts), n, 4, _cabi.ptr(rsd), 3, 20, None, 0.0, 3,
+                                                 _cabi.ptr(ws), nbytes, st) == 0
+        idx = torch.full((n, 20), -7, dtype=torch.int64, device=DEV)
+        dist = torch.zeros((n, 20), device=DEV)
+        assert _cabi.lib.fgc_knn_search(n, 4, 3, 20, 0, 0, 16, _cabi.ptr(idx), _cabi.ptr(dist), _cabi.ptr(ws),
+                                        nbytes, st) == 0
+        status = ctypes.c_int32(0)
+        assert _cabi.lib.fgc_read_status(_cabi.ptr(ws), ctypes.byref(status), st) == 0
+        assert status.value & _cabi.STATUS_INTERNAL and bool((idx == -7).all())
+    finally:
+        km.grid_dims = old
+        km._grid_memory.clear()
 
 
 def test_knn_gradient_on_reference_slot_order(golden_dir):
