@@ -33,7 +33,7 @@ FGC_MAX_K = 257
 KERNELS_BUILD_GRID = 13
 KERNELS_BUILD_GRID_D4 = 16      # D = 4: a second density pass may follow a fallback to three binned coordinates
 KERNELS_PUBLISH_STATUS = 1   # the wrapper's status check after the grid build
-KERNELS_SEARCH = 1
+KERNELS_SEARCH = 2             # k_knn + k_knn_hard (the queries that gave up their walk)
 KERNELS_KNN_BWD = 1
 KERNELS_KNN_BWD_SORTED = 7   # reverse graph (6) + gather (1)
 KERNELS_GRAVNET_FWD = 1

@@ -42,6 +42,7 @@ struct KnnGrid {
     int32_t n_big_cells;   // length of the work list of cells sorted by one warp each
     int32_t n_huge_cells;  // length of the work list of cells sorted by one CTA each
     int32_t stat_blocks_done;   // CTAs of the density pass that have added their share
+    int32_t n_hard;        // queries whose walk gave up in a large row split (searched by whole CTAs)
     unsigned long long sum_sq;   // sum over cells of (points in cell)^2, first grid
     // optional debug counters (filled when a search is launched with count_evals):
     // [0] distance evaluations, [1] 32-candidate steps, [2] list insertions,

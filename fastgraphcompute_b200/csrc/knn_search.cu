@@ -37,6 +37,7 @@ struct KnnArgs {
     const uint8_t *sflag;   // nullptr: no direction restriction
     const int *bounds;      // cell boundaries, total_bins + 1 entries
     const uint8_t *done;    // nullptr, or 1 where the tile kernel already wrote the row
+    int *hardlist;          // queries handed over to k_knn_hard (cell-order positions)
     KnnGrid *grid;
     int64_t *out_idx;
     float *out_dist;
@@ -55,6 +56,11 @@ struct KnnArgs {
 // residency) makes no measurable difference.
 constexpr int kKnnWarps = 8;
 constexpr uint32_t kInfBits = 0x7f800000u;
+// A query that walks mostly empty cells gives up and scans its whole row split.  In a row split
+// of more than kHardMin points that scan is thousands of steps for ONE warp, which then runs on
+// alone after every other query has finished; such queries are collected instead and searched
+// by a whole CTA each (k_knn_hard).
+constexpr int kHardMin = 4096;
 
 // Squared distance over NV float4 chunks.  Order and rounding: acc = acc + (a-b)*(a-b)
 // per dimension, dimension 0 first, no fused multiply-add; the first term needs no add.
@@ -384,7 +390,16 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
                 // walking mostly empty cells: scanning the whole row split is cheaper
                 if (items_done * 8 > (long long)n_e) { brute = true; break; }
             }
-            if (brute) list.init(lane, kn);
+            if (brute) {
+                if (n_e > kHardMin) {
+                    if (lane == 0) {
+                        a.hardlist[atomicAdd(&g->n_hard, 1)] = qi;
+                        if (COUNT) atomicAdd(&g->counters[5], 1ull);
+                    }
+                    return;             // k_knn_hard writes this row
+                }
+                list.init(lane, kn);
+            }
         }
         if (brute) {
             if (COUNT) cnt_brute = 1;
@@ -434,6 +449,89 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
     }
 }
 
+// The queries that gave up their walk in a large row split: one CTA per query, every warp scans
+// an interleaved eighth of the row split with a list of its own, warp 0 then offers the other
+// warps' lists to its own and writes the row.  Same candidates, same strict "<" rule, fixed
+// order: the result does not depend on which CTA picks the query up.
+template <int NV, int R>
+__global__ void __launch_bounds__(kKnnWarps * 32)
+k_knn_hard(const KnnArgs a)
+{
+    __shared__ float s_d[kKnnWarps][R * 32];
+    __shared__ int s_i[kKnnWarps][R * 32];
+    const int lane = threadIdx.x & 31;
+    const int wib = threadIdx.x >> 5;
+    KnnGrid *__restrict__ g = a.grid;
+    if (g->status != 0) return;
+    const int n_hard = g->n_hard;
+    const int K = a.K, kn = K - 1, nc = a.n_coords;
+    const uint8_t *__restrict__ sflag = a.sflag;
+    for (int h = blockIdx.x; h < n_hard; h += gridDim.x) {
+        const int qi = a.hardlist[h];
+        float4 q[NV];
+#pragma unroll
+        for (int v = 0; v < NV; v++) q[v] = __ldg(a.scoords + (size_t)qi * NV + v);
+        const int B = g->B;
+        const int e = __ldg(a.sbin + qi) / B;
+        const int ev_begin = __ldg(a.bounds + e * B);
+        const int n_e = __ldg(a.bounds + (e + 1) * B) - ev_begin;
+        NeighbourList<R> list;
+        list.init(lane, kn);
+        auto offer_all = [&](float dc, int j) {
+            unsigned m = __ballot_sync(FGC_FULL_MASK, __float_as_uint(dc) < list.tau);
+            while (m) {
+                const int src = __ffs(m) - 1;
+                m &= m - 1;
+                list.offer(lane, __shfl_sync(FGC_FULL_MASK, dc, src), __shfl_sync(FGC_FULL_MASK, j, src));
+            }
+        };
+        for (int t = wib * 32; t < n_e; t += kKnnWarps * 32) {
+            const int j = ev_begin + t + lane;
+            float dc = __uint_as_float(kInfBits);
+            if (t + lane < n_e) {
+                float4 c[NV];
+#pragma unroll
+                for (int v = 0; v < NV; v++) c[v] = __ldg(a.scoords + (size_t)j * NV + v);
+                bool ok = j != qi;
+                if (sflag) { const uint8_t f = sflag[j]; ok = ok && f != 1 && f != 2; }
+                if (ok) dc = dist_sq<NV>(q, c, nc);
+            }
+            offer_all(dc, j);
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            s_d[wib][r * 32 + lane] = list.d[r];
+            s_i[wib][r * 32 + lane] = list.id[r];
+        }
+        __syncthreads();
+        if (wib == 0) {
+            for (int w = 1; w < kKnnWarps; w++)
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const int j = s_i[w][r * 32 + lane];
+                    // slots that are empty or not part of the list carry id -1
+                    const float dc = j >= 0 ? s_d[w][r * 32 + lane] : __uint_as_float(kInfBits);
+                    offer_all(dc, j);
+                }
+            const int orig_q = __ldg(a.sorig + qi);
+            int64_t *__restrict__ out_i = a.out_idx + (size_t)orig_q * K;
+            float *__restrict__ out_d = a.out_dist + (size_t)orig_q * K;
+            if (lane == 0) { out_i[0] = orig_q; out_d[0] = 0.f; }
+            const int64_t pad = a.tf_compat ? (int64_t)orig_q : (int64_t)-1;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const int s = lane * R + r;
+                if (s < kn) {
+                    const bool filled = __float_as_uint(list.d[r]) < kInfBits && list.id[r] >= 0;
+                    out_i[1 + s] = filled ? (int64_t)__ldg(a.sorig + list.id[r]) : pad;
+                    out_d[1 + s] = filled ? list.d[r] : 0.f;
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // MODE 0: grid over three coordinates (D <= 3); 1: over four (D >= 5); 2: D = 4, where the grid
 // build decides on the device between the two -- one launch, one uniform branch (two launches
 // of which one returns at once cost the same; out-of-line bodies were slower).
@@ -465,6 +563,13 @@ static int launch_knn_nv(const KnnArgs &a, cudaStream_t s)
         else if (R <= 4) k_knn<NV, 4, false, G4><<<blocks, T, 0, s>>>(a);
         else k_knn<NV, 8, false, G4><<<blocks, T, 0, s>>>(a);
     }
+    FGC_CHECK_LAUNCH();
+    // the queries that gave up their walk (usually none: the CTAs return at once)
+    const unsigned hard_blocks = 148 * 2;
+    if (R <= 1) k_knn_hard<NV, 1><<<hard_blocks, T, 0, s>>>(a);
+    else if (R <= 2) k_knn_hard<NV, 2><<<hard_blocks, T, 0, s>>>(a);
+    else if (R <= 4) k_knn_hard<NV, 4><<<hard_blocks, T, 0, s>>>(a);
+    else k_knn_hard<NV, 8><<<hard_blocks, T, 0, s>>>(a);
     return (int)cudaGetLastError();
 }
 template <int NV>
@@ -508,6 +613,7 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     a.sflag = has_direction ? (const uint8_t *)(ws + L.sflag) : nullptr;
     a.bounds = (const int *)(ws + L.counts);
     a.done = use_tiles ? (const uint8_t *)(ws + L.done) : nullptr;
+    a.hardlist = (int *)(ws + L.stmp);        // free since the grid build
     a.grid = (KnnGrid *)(ws + L.header);
     a.out_idx = out_idx;
     a.out_dist = out_distsq;
