@@ -388,6 +388,7 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
                 if (!any) break;
                 if (list.tau < kInfBits && fd * fd > __uint_as_float(list.tau) * 1.00001f) break;
                 // walking mostly empty cells: scanning the whole row split is cheaper
+                // (giving up earlier costs more than it saves once row splits have millions of points)
                 if (items_done * 8 > (long long)n_e) { brute = true; break; }
             }
             if (brute) {
