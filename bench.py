@@ -171,23 +171,28 @@ def cpu_reference_fwd_bwd(workload, torch):
     return time.perf_counter() - t0, "port"
 
 
+def load_synthetic_standalone():
+    """The workload generators, loaded from their file without importing the package around them
+    (the package loads the CUDA library on import; the reference arm must not map it)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "fgc_bench_synthetic", os.path.join(ROOT, "fastgraphcompute_b200", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod       # dataclasses looks the defining module up by name
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def run_reference(args):
+    """The reference's own CPU ops on the full headline workload, every step the same 200 000
+    points as the GPU arm (about 4 s per step on one core; its loops are single-threaded)."""
     rank = env_int("RANK", 0)
     if rank != 0:
         return
     import torch
-    from fastgraphcompute_b200 import synthetic
-    full = synthetic.c2_gaussian_mixture()
-    # bound the whole run to a few minutes: probe once, then shrink the per-step sample if needed
-    probe = synthetic.c2_gaussian_mixture(scale=0.1)
-    t_probe, kind = cpu_reference_fwd_bwd(probe, torch)
-    est_full = t_probe * 12.0          # cost per point grows with the event size
-    budget = 200.0
-    total_steps = args.steps + args.warmup
-    scale = 1.0
-    if est_full * total_steps > budget:
-        scale = max(0.05, min(1.0, budget / (est_full * total_steps)))
-    w = full if scale == 1.0 else synthetic.c2_gaussian_mixture(scale=scale)
+    synthetic = load_synthetic_standalone()
+    w = synthetic.c2_gaussian_mixture()
+    kind = "reference"
     for _ in range(args.warmup):
         cpu_reference_fwd_bwd(w, torch)
     times = []
@@ -196,8 +201,7 @@ def run_reference(args):
         times.append(t)
     total = sum(times)
     value = w.n_points * args.steps / total
-    sample = "%d of %d points per step (same generator, scale %.3g), %d steps" % (
-        w.n_points, full.n_points, scale, args.steps)
+    sample = "the full workload every step (%d points, forward + backward), %d steps" % (w.n_points, args.steps)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -273,19 +277,11 @@ def run_b200(args):
     sampler = ClockSampler(gpu_identifier(torch, local_rank)) if rank == 0 else None
 
     # ---- device-resident timing ("value") ----------------------------------------------------
-    search_events = []
-
-    def hook(tag):
-        e = torch.cuda.Event(enable_timing=True)
-        e.record()
-        search_events.append((tag, e))
-
     for _ in range(max(args.warmup, 3)):
         flush.zero_()
         step_resident()
     barrier()
     t_load0 = time.time()
-    knn_mod.phase_hook = hook
     pairs = []
     for _ in range(args.steps):
         flush.zero_()                       # evict the 3.2 MB inputs and the outputs from L2
@@ -295,15 +291,46 @@ def run_b200(args):
         step_resident(mark=True)
         e1.record()
         pairs.append((e0, e1))
-    knn_mod.phase_hook = None
     barrier()
     t_load1 = time.time()
     step_ms = [a.elapsed_time(b) for a, b in pairs]
     total_ms = max_over_ranks(sum(step_ms))
     value = world * n * args.steps / (total_ms * 1e-3)
-    begins = [e for t, e in search_events if t == "search_begin"]
-    ends = [e for t, e in search_events if t == "search_end"]
-    knn_ms = [a.elapsed_time(b) for a, b in zip(begins, ends)]
+
+    # The dominant kernel alone, for the roofline: the search half of the forward through the
+    # split C ABI (fgc_knn_build_grid_dims once, then fgc_knn_search per step on that grid; the
+    # grid form is the one the public call settles on for this data), same inputs, L2 flushed
+    # before every launch, CUDA events on the launching stream around the launch.
+    def time_search_kernel(reps):
+        nb = _cabi.lib.fgc_knn_workspace_bytes(n, d_coords.shape[1], d_rs.numel(), K)
+        ws = torch.empty(nb, dtype=torch.uint8, device=dev)
+        s_idx = torch.empty((n, K), dtype=torch.int64, device=dev)
+        s_dsq = torch.empty((n, K), dtype=torch.float32, device=dev)
+        stream = _cabi.current_stream(dev)
+        info = torch.empty(2, dtype=torch.int32, pin_memory=True)
+        _cabi.check(_cabi.lib.fgc_knn_build_grid_dims(_cabi.ptr(d_coords), n, d_coords.shape[1], _cabi.ptr(d_rs),
+                                                      d_rs.numel(), K, None, 0.0, 0, _cabi.ptr(ws), nb, stream), "build")
+        _cabi.check(_cabi.lib.fgc_knn_publish_grid_info(_cabi.ptr(ws), info.data_ptr(), stream), "info")
+        torch.cuda.synchronize(dev)
+        form = int(info[1]) & 15
+        _cabi.check(_cabi.lib.fgc_knn_build_grid_dims(_cabi.ptr(d_coords), n, d_coords.shape[1], _cabi.ptr(d_rs),
+                                                      d_rs.numel(), K, None, 0.0, form, _cabi.ptr(ws), nb, stream), "build")
+        flags = 8 if form == 3 else 16 if form == 4 else 0
+        out = []
+        for i in range(reps + 2):
+            flush.zero_()
+            a0 = torch.cuda.Event(enable_timing=True)
+            a1 = torch.cuda.Event(enable_timing=True)
+            a0.record()
+            _cabi.check(_cabi.lib.fgc_knn_search(n, d_coords.shape[1], d_rs.numel(), K, 0, 0, flags, _cabi.ptr(s_idx),
+                                                 _cabi.ptr(s_dsq), _cabi.ptr(ws), nb, stream), "search")
+            a1.record()
+            if i >= 2:
+                out.append((a0, a1))
+        torch.cuda.synchronize(dev)
+        return [a.elapsed_time(b) for a, b in out]
+
+    knn_ms = time_search_kernel(args.steps)
     knn_ms_avg = sum(knn_ms) / len(knn_ms)
     phases = {"fwd_ms_median": statistics.median(a.elapsed_time(m_) for (a, _), m_ in zip(pairs, fwd_marks)),
               "bwd_ms_median": statistics.median(m_.elapsed_time(b) for (_, b), m_ in zip(pairs, fwd_marks)),
@@ -667,7 +694,7 @@ def run_b200(args):
                                "peak_source": "of " + peak_oc_kind}}
 
     # ---- the reference's own published kNN timings, same configurations ------------------------
-    # (BASELINE.md section 1: forward only, one event, timer around the public call plus a device
+    # (forward only, one event, timer around the public call plus a device
     # synchronise as in performance/generate_faiss_performance.py:68-92; the published figures
     # come from an unspecified GPU and are quoted for orientation, not as a like-for-like ratio)
     published = None

@@ -181,7 +181,7 @@ extern "C" int fgc_bin_prepare(const float *coords, int64_t n_vert, int32_t n_co
     if (n_vert > 0) {
         const int64_t total = n_vert * n_coords;
         int blocks = (int)fgc::ceil_div64(total, (int64_t)fgc::kReduceThreads * 8);
-        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (blocks > fgc::sm_count() * 8) blocks = fgc::sm_count() * 8;
         if (blocks < 1) blocks = 1;
         fgc::k_bin_minmax<<<blocks, fgc::kReduceThreads, 0, s>>>(coords, n_vert, n_coords, out_params);
         FGC_CHECK_LAUNCH();

@@ -19,6 +19,22 @@
 
 namespace fgc {
 
+// Number of SMs of the current device (148 on a B200), asked once per device and kept.  Grids of
+// grid-stride kernels are sized in multiples of it.  A failed query falls back to 148 so that no
+// launch path has to handle an error here.
+inline int sm_count()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    int n = cached[dev];
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;   // racing writers store the same value
+    }
+    return n;
+}
+
 __host__ __device__ inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 

@@ -34,7 +34,7 @@ extern "C" int fgc_index_replacer(const int64_t *to_be_replaced, int64_t n,
     if (n == 0) return FGC_OK;
     if (!to_be_replaced || !out || (n_replacements > 0 && !replacements)) return FGC_ERR_BAD_ARGUMENT;
     int64_t blocks = fgc::ceil_div64(n, 256 * 4);
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > fgc::sm_count() * 16) blocks = fgc::sm_count() * 16;
     if (blocks < 1) blocks = 1;
     fgc::k_index_replacer<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
         to_be_replaced, n, replacements, n_replacements, out);

@@ -575,7 +575,7 @@ extern "C" int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int3
     if (bins_target < 1) bins_target = 1;
 
     const int pt_blocks = (n + 255) / 256;
-    const int red_blocks = pt_blocks < 148 * 4 ? pt_blocks : 148 * 4;
+    const int red_blocks = pt_blocks < fgc::sm_count() * 4 ? pt_blocks : fgc::sm_count() * 4;
     k_minmax<<<red_blocks, 256, 0, s>>>(coords, n, n_coords, n_bin_dims, grid);
     FGC_CHECK_LAUNCH();
     k_grid_setup<<<1, 32, 0, s>>>(grid, row_splits, (int)n_rs, n, n_bin_dims, bins_target, bins_cap);
@@ -584,26 +584,26 @@ extern "C" int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int3
     // largest table k_grid_setup may choose and surplus blocks return at once.
     const int64_t max_entries = (int64_t)bins_cap * n_events + 1;
     const int scan_blocks = (int)ceil_div64(max_entries, kScanTile);
-    k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid, 0);
+    k_zero_counts<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, 0);
     FGC_CHECK_LAUNCH();
     k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
                                           pbin, prank, 0);
     FGC_CHECK_LAUNCH();
     if (adaptive) {
         const int allow_fallback = n_coords == 4 && forced == 0;
-        k_cell_stat_refine<<<148 * 4, 256, 0, s>>>(counts, grid, n, seen_target, seen_target3, bins_target, 0,
+        k_cell_stat_refine<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, n, seen_target, seen_target3, bins_target, 0,
                                                     allow_fallback);
         FGC_CHECK_LAUNCH();
-        k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid, 1);
+        k_zero_counts<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, 1);
         FGC_CHECK_LAUNCH();
         k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
                                               pbin, prank, 1);
         FGC_CHECK_LAUNCH();
         if (allow_fallback) {
             // second density pass: runs only when the first one fell back to three coordinates
-            k_cell_stat_refine<<<148 * 4, 256, 0, s>>>(counts, grid, n, seen_target, seen_target3, bins_target, 1, 0);
+            k_cell_stat_refine<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, n, seen_target, seen_target3, bins_target, 1, 0);
             FGC_CHECK_LAUNCH();
-            k_zero_counts<<<148 * 4, 256, 0, s>>>(counts, grid, 2);
+            k_zero_counts<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, 2);
             FGC_CHECK_LAUNCH();
             k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
                                                   pbin, prank, 2);
@@ -621,8 +621,8 @@ extern "C" int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int3
     k_rank_place<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, L.nv, direction_or_null, grid, counts, pbin,
                                            prank, stmp, sorig, scoords, sbin, sflag, biglist, hugelist);
     FGC_CHECK_LAUNCH();
-    const int n_warp_blocks = 148 * 4;
-    k_sort_large_cells<<<n_warp_blocks + 148, kSortWarps * 32, 0, s>>>(
+    const int n_warp_blocks = fgc::sm_count() * 4;
+    k_sort_large_cells<<<n_warp_blocks + fgc::sm_count(), kSortWarps * 32, 0, s>>>(
         coords, n_coords, L.nv, direction_or_null, grid, counts, biglist, hugelist, n_warp_blocks, sorig,
         scoords, sbin, sflag);
     FGC_CHECK_LAUNCH();

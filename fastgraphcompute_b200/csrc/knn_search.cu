@@ -26,7 +26,6 @@
 // points is kept.
 #include "knn_grid.cuh"
 #include "shell_table.cuh"
-#include "knn_tile.cuh"
 
 namespace fgc {
 
@@ -36,7 +35,6 @@ struct KnnArgs {
     const int *sbin;
     const uint8_t *sflag;   // nullptr: no direction restriction
     const int *bounds;      // cell boundaries, total_bins + 1 entries
-    const uint8_t *done;    // nullptr, or 1 where the tile kernel already wrote the row
     int *hardlist;          // queries handed over to k_knn_hard (cell-order positions)
     KnnGrid *grid;
     int64_t *out_idx;
@@ -154,12 +152,23 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
     const int wib = threadIdx.x >> 5;
     const int qi = blockIdx.x * kKnnWarps + wib;   // position in cell order
     KnnGrid *__restrict__ g = a.grid;
-    if (qi >= a.n_vert || g->status != 0) return;
+    if (qi >= a.n_vert) return;
+    if (g->status != 0) {
+        // Bad input (non-finite coordinate, malformed row splits): the grid was not built.  Every
+        // row gets the defaults of a point without neighbours, so that a caller who does not look
+        // at the status word never reads uninitialised indices.
+        const int K = a.K;
+        const int64_t pad = a.tf_compat ? (int64_t)qi : (int64_t)-1;
+        for (int s = lane; s < K; s += 32) {
+            a.out_idx[(size_t)qi * K + s] = s == 0 ? (int64_t)qi : pad;
+            a.out_dist[(size_t)qi * K + s] = 0.f;
+        }
+        return;
+    }
     if ((g->gdims == 4) != G4) {            // built in the other form: never walk it
         if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(&g->status, FGC_STATUS_INTERNAL);
         return;
     }
-    if (a.done && a.done[qi]) return;
 
     const int K = a.K, kn = K - 1;
     const int nc = a.n_coords;
@@ -393,11 +402,16 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
             }
             if (brute) {
                 if (n_e > kHardMin) {
+                    // (the list holds n_vert entries and every query appends at most once per
+                    // search, so the bound below only guards against a stale counter)
+                    int slot = 0;
                     if (lane == 0) {
-                        a.hardlist[atomicAdd(&g->n_hard, 1)] = qi;
+                        slot = atomicAdd(&g->n_hard, 1);
+                        if (slot < a.n_vert) a.hardlist[slot] = qi;
                         if (COUNT) atomicAdd(&g->counters[5], 1ull);
                     }
-                    return;             // k_knn_hard writes this row
+                    slot = __shfl_sync(FGC_FULL_MASK, slot, 0);
+                    if (slot < a.n_vert) return;             // k_knn_hard writes this row
                 }
                 list.init(lane, kn);
             }
@@ -464,7 +478,7 @@ k_knn_hard(const KnnArgs a)
     const int wib = threadIdx.x >> 5;
     KnnGrid *__restrict__ g = a.grid;
     if (g->status != 0) return;
-    const int n_hard = g->n_hard;
+    const int n_hard = min(g->n_hard, a.n_vert);
     const int K = a.K, kn = K - 1, nc = a.n_coords;
     const uint8_t *__restrict__ sflag = a.sflag;
     for (int h = blockIdx.x; h < n_hard; h += gridDim.x) {
@@ -566,29 +580,13 @@ static int launch_knn_nv(const KnnArgs &a, cudaStream_t s)
     }
     FGC_CHECK_LAUNCH();
     // the queries that gave up their walk (usually none: the CTAs return at once)
-    const unsigned hard_blocks = 148 * 2;
+    const unsigned hard_blocks = fgc::sm_count() * 2;
     if (R <= 1) k_knn_hard<NV, 1><<<hard_blocks, T, 0, s>>>(a);
     else if (R <= 2) k_knn_hard<NV, 2><<<hard_blocks, T, 0, s>>>(a);
     else if (R <= 4) k_knn_hard<NV, 4><<<hard_blocks, T, 0, s>>>(a);
     else k_knn_hard<NV, 8><<<hard_blocks, T, 0, s>>>(a);
     return (int)cudaGetLastError();
 }
-template <int NV>
-static int launch_tiles(const KnnTileArgs &t, bool count, cudaStream_t s)
-{
-    const int tiles = (t.n_vert + 31) / 32;
-    const unsigned blocks = (unsigned)((tiles + kTileWarps - 1) / kTileWarps);
-    const size_t smem = sizeof(float) * (size_t)tile_smem_words(t.K - 1) * kTileWarps;
-    if (count) {
-        FGC_RETURN_IF_CUDA(cudaFuncSetAttribute(k_knn_tile<NV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k_knn_tile<NV, true><<<blocks, kTileWarps * 32, smem, s>>>(t);
-    } else {
-        FGC_RETURN_IF_CUDA(cudaFuncSetAttribute(k_knn_tile<NV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k_knn_tile<NV, false><<<blocks, kTileWarps * 32, smem, s>>>(t);
-    }
-    return (int)cudaGetLastError();
-}
-
 }  // namespace fgc
 
 extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
@@ -605,15 +603,12 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     cudaStream_t s = (cudaStream_t)stream;
     char *ws = (char *)workspace;
     const bool count = (flags & FGC_SEARCH_COUNT) != 0;
-    // the tile pass knows grids over three coordinates only
-    const bool use_tiles = (flags & FGC_SEARCH_TILES) && K >= 2 && K - 1 <= kTileMaxNeighbours && n_coords <= 3;
     KnnArgs a;
     a.scoords = (const float4 *)(ws + L.scoords);
     a.sorig = (const int *)(ws + L.sorig);
     a.sbin = (const int *)(ws + L.sbin);
     a.sflag = has_direction ? (const uint8_t *)(ws + L.sflag) : nullptr;
     a.bounds = (const int *)(ws + L.counts);
-    a.done = use_tiles ? (const uint8_t *)(ws + L.done) : nullptr;
     a.hardlist = (int *)(ws + L.stmp);        // free since the grid build
     a.grid = (KnnGrid *)(ws + L.header);
     a.out_idx = out_idx;
@@ -623,19 +618,10 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     a.n_coords = n_coords;
     a.tf_compat = tf_compat;
     a.count_evals = count;
-    if (use_tiles) {
-        // optional first pass: tiles of 32 neighbouring queries that share their candidates; it
-        // marks the rows it completed and the pass below searches the remaining queries.
-        KnnTileArgs t;
-        t.scoords = a.scoords; t.sorig = a.sorig; t.sbin = a.sbin; t.sflag = a.sflag;
-        t.bounds = a.bounds; t.grid = a.grid;
-        t.out_idx = out_idx; t.out_dist = out_distsq;
-        t.done = (uint8_t *)(ws + L.done);
-        t.n_vert = (int)n_vert; t.K = K; t.n_coords = n_coords; t.tf_compat = tf_compat;
-        const int trc = L.nv == 1 ? launch_tiles<1>(t, count, s) : launch_tiles<2>(t, count, s);
-        if (trc != 0) return trc;
-        if (flags & 4) return FGC_OK;   // timing aid: tile pass alone (rows of other queries stay unwritten)
-    }
+    // Every search starts its own list of queries for k_knn_hard: a grid may be searched more
+    // than once (the build/search split), and a count left by an earlier search would make
+    // this one re-scan stale entries and append behind them.
+    FGC_RETURN_IF_CUDA(cudaMemsetAsync(&a.grid->n_hard, 0, sizeof(int32_t), s));
     if (n_coords <= 3) return launch_knn_nv<1, 0>(a, s);
     if (L.nv == 1) {
         // D = 4: a caller that fixed the grid's form at build time says so here too and gets the

@@ -359,7 +359,7 @@ extern "C" int fgc_oc_fill(const void *workspace, size_t workspace_bytes, int64_
     if (m_total > 0) {
         if (!out_M) return FGC_ERR_BAD_ARGUMENT;
         int64_t blocks = ceil_div64(m_total, 256);
-        if (blocks > 148 * 64) blocks = 148 * 64;
+        if (blocks > fgc::sm_count() * 64) blocks = fgc::sm_count() * 64;
         k_oc_fill_m<<<(unsigned)blocks, 256, 0, s>>>(vals, obj_start, n_unique, n_maxuq, out_M);
         FGC_CHECK_LAUNCH();
     }
@@ -367,7 +367,7 @@ extern "C" int fgc_oc_fill(const void *workspace, size_t workspace_bytes, int64_
         if (n_maxrs > 0x7fffffff) return FGC_ERR_TOO_LARGE;
         const int64_t runs = n_unique * ceil_div64(n_maxrs, kOcTile * kOcRun);
         int64_t blocks = ceil_div64(runs, 8);           // 8 warps per CTA, one run of tiles per warp and pass
-        if (blocks > 148 * 32) blocks = 148 * 32;
+        if (blocks > fgc::sm_count() * 32) blocks = fgc::sm_count() * 32;
         if ((n_maxrs & 1) == 0 && ((uintptr_t)out_M_not_or_null & 15) == 0)
             k_oc_fill_m_not<true><<<(unsigned)blocks, 256, 0, s>>>(vals, obj_start, obj_split, row_splits, n_unique,
                                                                    (int)n_maxrs, out_M_not_or_null);
@@ -391,7 +391,7 @@ extern "C" int fgc_select_with_default(const int64_t *idx, int64_t n_idx, const 
     if (!idx || !out || (!feat && n_rows_feat > 0)) return FGC_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     int64_t blocks = ceil_div64(total, 256);
-    if (blocks > 148 * 64) blocks = 148 * 64;
+    if (blocks > fgc::sm_count() * 64) blocks = fgc::sm_count() * 64;
     if (word_bytes == 4) {
         uint32_t w;
         memcpy(&w, default_word_host, 4);

@@ -131,7 +131,7 @@ extern "C" int fgc_build_reverse_graph(const int64_t *idx, int64_t n_vert, int32
     // offsets and cursor are adjacent: one clear for both
     FGC_RETURN_IF_CUDA(cudaMemsetAsync(offsets, 0, L.blocksums - L.offsets, s));
     int64_t blocks = ceil_div64(total, 256 * 4);
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > fgc::sm_count() * 16) blocks = fgc::sm_count() * 16;
     k_rev_count<<<(unsigned)blocks, 256, 0, s>>>(idx, total, n, offsets);
     FGC_CHECK_LAUNCH();
     const int scan_blocks = (int)ceil_div64(n_vert + 1, kScanTile);

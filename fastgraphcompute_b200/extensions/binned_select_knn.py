@@ -20,9 +20,6 @@ target_occupancy = 0.0
 # call fully asynchronous but turns bad inputs (NaN, malformed row_splits) into
 # silently unwritten outputs.
 check_status = True
-# True adds the tile pass (32 neighbouring queries per warp sharing their candidates) before the
-# warp-per-query pass.  Same results; measured slower than the default on B200 so far.
-use_tiles = False
 # Backward by sorted-segment reductions over a reverse neighbour graph instead of float atomics:
 # bit-identical gradients from run to run (the atomic version, like the reference's CUDA path,
 # sums in arrival order).  Falls back to the atomic kernel when N*K >= 2^31.
@@ -51,10 +48,6 @@ def _raise_for_status(status):
 grid_dims = 0
 grid_probe_every = 64
 _grid_memory = {}        # (device, N, row splits, K) -> [form, calls since the last automatic choice]
-
-# Optional instrumentation: a callable(tag) invoked on the launching stream right before and
-# after the search kernel ("search_begin" / "search_end"); benchmarks record CUDA events here.
-phase_hook = None
 
 
 def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=False):
@@ -99,15 +92,11 @@ def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=Fal
                         "fgc_knn_publish_grid_info")
             status_ready = torch.cuda.Event()
             status_ready.record()
-        if phase_hook is not None:
-            phase_hook("search_begin")
         _cabi.check(_cabi.lib.fgc_knn_search(
             n_vert, n_coords, n_rs, K, int(direction is not None), int(bool(tf_compat)),
-            (1 if count_evals else 0) | (2 if use_tiles else 0) | (8 if form == 3 else 16 if form == 4 else 0),
+            (1 if count_evals else 0) | (8 if form == 3 else 16 if form == 4 else 0),
             _cabi.ptr(idx), _cabi.ptr(dist),
             _cabi.ptr(ws), nbytes, stream), "fgc_knn_search")
-        if phase_hook is not None:
-            phase_hook("search_end")
         if status_host is not None:
             status_ready.synchronize()
             info = status_host.tolist()

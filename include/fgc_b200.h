@@ -16,8 +16,10 @@
  *    positive cudaError_t value.  Data-dependent problems (non-finite
  *    coordinates, malformed row_splits) are reported through a status word in
  *    device memory, read with fgc_read_status().
- *  - Re-entrant: no global mutable state; concurrent calls on different
- *    streams/devices are safe as long as they use different workspaces.
+ *  - Re-entrant: concurrent calls on different streams/devices are safe as long
+ *    as they use different workspaces.  The library keeps no mutable state
+ *    between calls, with one exception: fgc_binned_knn_fwd_static owns a scratch
+ *    array per GPU that all of its calls share (see there).
  *
  * Each entry point names the reference interface it replaces
  * (paths relative to the FastGraphCompute repository).
@@ -154,9 +156,14 @@ int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,
  * (extensions/binned_select_knn_cuda_kernel.cu:252-384) + index_replacer + un-sort
  * scatter (extensions/binned_knn_autograd_kernel.cpp:157-195).  has_direction must say
  * whether the grid was built with a direction array.  flags: FGC_SEARCH_COUNT accumulates
- * the debug counters in the workspace (fgc_knn_read_counters); FGC_SEARCH_TILES adds a
- * first pass in which tiles of 32 neighbouring queries share their candidates (one query per
- * lane, heaps in shared memory; same results, currently slower than the default on B200).
+ * the debug counters in the workspace (fgc_knn_read_counters).  A built grid may be searched
+ * any number of times (other K is not allowed: the workspace layout depends on the arguments).
+ *
+ * When the status word of the workspace is non-zero after the grid build (non-finite
+ * coordinate, malformed row_splits; see fgc_read_status) no neighbour is searched: every row
+ * of out_idx / out_distsq gets the defaults of a point without neighbours (itself in slot 0,
+ * -1 -- or itself with tf_compat -- elsewhere, distances 0).  The same holds for
+ * fgc_binned_knn_fwd and fgc_binned_knn_fwd_static.
  */
 int fgc_knn_build_grid(const float *coords, int64_t n_vert, int32_t n_coords,
                        const int64_t *row_splits, int64_t n_rs, int32_t K,
@@ -179,7 +186,6 @@ int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int32_t n_coord
                             fgc_stream_t stream);
 int fgc_knn_publish_grid_info(const void *workspace, int32_t *info_mapped, fgc_stream_t stream);
 #define FGC_SEARCH_COUNT 1     /* flags: accumulate the debug counters */
-#define FGC_SEARCH_TILES 2     /* flags: run the tile pass before the warp-per-query pass */
 #define FGC_SEARCH_GRID3 8     /* flags: the grid was built with grid_dims = 3 (D = 4) */
 #define FGC_SEARCH_GRID4 16    /* flags: the grid was built with grid_dims = 4 (D = 4) */
 int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
@@ -191,8 +197,8 @@ int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
  * Diagnostics of a workspace, copied to the host (synchronises the stream): eight 64-bit
  * counters that a search launched with FGC_SEARCH_COUNT accumulates ([0] distance
  * evaluations, [1] 32-candidate steps, [2] list insertions, [3] metadata batches, [4] shells,
- * [5] queries that scanned their whole row split, [6] queries finished by the tile pass,
- * [7] eligible tiles), the grid shape [3] and the cell width.
+ * [5] queries that scanned their whole row split, [6] and [7] unused), the grid shape [3] and
+ * the cell width.
  * Any output pointer may be NULL.  No counterpart in the reference.
  */
 int fgc_knn_read_counters(const void *workspace, uint64_t *counters_host,
@@ -209,14 +215,20 @@ int fgc_knn_read_counters(const void *workspace, uint64_t *counters_host,
  * (FGC_STATIC_WORKSPACE_BYTES per GPU, held by every GPU that loads the library until the
  * process exits).  Same inputs, outputs and results as fgc_binned_knn_fwd, plus
  *   out_status : [1] int32 in device memory, receives the FGC_STATUS_* word of the call.
+ *                It is written only when the function returns FGC_OK; after any other
+ *                return value its content is whatever it held before.
  * Limits and rules:
  *   - returns FGC_ERR_STATIC_TOO_LARGE when fgc_knn_workspace_bytes(n_vert, n_coords, n_rs, K)
  *     exceeds FGC_STATIC_WORKSPACE_BYTES (that is at about 40 000 points with up to 4
  *     coordinates and about 35 000 with 5 to 8); nothing is launched in that case;
  *   - calls no cudaMalloc/cudaFree or other allocating routine;
  *   - the first call on each GPU looks up the device address of the array
- *     (cudaGetSymbolAddress, with that GPU current); make that first call outside any
- *     stream capture;
+ *     (cudaGetSymbolAddress, with that GPU current).  With CUDA's lazy module loading that
+ *     call may also load the library's device code, which places the array in device memory
+ *     and can synchronise.  A host that must not see either later makes one warm-up call
+ *     per GPU at start-up (n_vert = 0 is enough), outside any stream capture;
+ *   - the GPU that owns `stream` and the pointers must be the current device: the array's
+ *     address is taken for the current device, not derived from the stream;
  *   - all calls on one GPU share the one array: calls that can overlap on the GPU (different
  *     streams or host threads) race and must be serialised by the caller.  The array keeps
  *     the previous call's contents; each call clears the parts it relies on being zero.

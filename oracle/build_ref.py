@@ -43,7 +43,9 @@ CPU_SOURCES = [
 
 
 def default_reference_root():
-    return os.environ.get("FGC_REFERENCE_ROOT", "/root/reference")
+    """Checkout of the reference: $FGC_REFERENCE_ROOT, else a directory named ``reference``
+    beside this repository."""
+    return os.environ.get("FGC_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def build(reference_root=None, force=False, verbose=True):

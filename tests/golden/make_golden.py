@@ -19,7 +19,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 
 import cases  # noqa: E402
-from oracle import ref_ops  # noqa: E402
+from oracle import build_ref, ref_ops  # noqa: E402
 from fastgraphcompute_b200 import synthetic  # noqa: E402
 
 
@@ -172,7 +172,7 @@ def main():
         print("binning", name)
     # the reference's own fixture (tests/test_bbc_data.npy, detector-like coordinates),
     # binned as its smoke test does (n_bins = 21, one row split)
-    fixture = os.path.join(ref_ops.__dict__.get("_REFERENCE_ROOT", "/root/reference"), "tests", "test_bbc_data.npy")
+    fixture = os.path.join(build_ref.default_reference_root(), "tests", "test_bbc_data.npy")
     if os.path.exists(fixture):
         data = np.load(fixture).astype(np.float32)
         r = ref_ops.ref_bin_by_coordinates(torch.tensor(data), torch.tensor([0, data.shape[0]]),

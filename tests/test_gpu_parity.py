@@ -543,26 +543,6 @@ def test_gravnet_shape_sweep():
                     assert dsq.shape == (100, k) and space.shape == (100, s)
 
 
-def test_knn_tile_pass_golden(golden_dir):
-    """The optional tile pass (32 neighbouring queries per warp) must give the same rows."""
-    import importlib
-    km = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
-    km.use_tiles = True
-    try:
-        for name, c in load(golden_dir, "knn").items():
-            i = c["in"]
-            coords, idx, dist = run_knn(i)
-            tf = "tf_compat" in i and bool(i["tf_compat"])
-            parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), c["out"]["idx"],
-                                     c["out"]["distsq"], pad_self=tf, what="tiles " + name)
-        w = synthetic.c2_gaussian_mixture(scale=0.15)
-        idx, dist = fgc.binned_select_knn(w.K, w.coords.to(DEV), w.row_splits.to(DEV))
-        oidx, odist = oracle.binned_select_knn(w.K, w.coords.numpy(), w.row_splits.numpy())
-        parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), oidx, odist, what="tiles c2")
-    finally:
-        km.use_tiles = False
-
-
 def test_knn_backward_sorted_segments_is_bit_reproducible(golden_dir):
     """The sorted-segment backward: same gradients as the oracle, identical bits on every run."""
     import importlib
