@@ -569,9 +569,12 @@ def run_b200(args):
                        "steps": 5, "warmup": 3}
 
     # ---- event-batched workload C3 sharded by event over the ranks (strong scaling) ----------
-    # Every rank holds the batch, searches the events the partition table gives it (no
-    # collective) and, with more than one rank, gathers the rows of all ranks (the one
-    # exchange step of the multi-GPU path).
+    # Every rank holds the batch and searches the events the partition table gives it.  Three
+    # ways to end: rows stay on the rank that computed them (no collective), rows of all ranks on
+    # every rank, rows of all ranks on rank 0.  The exchange is per-event point-to-point blocks
+    # straight into the final tensors, ids as int32 on the wire, events searched in three groups
+    # so that finished rows travel while the next group is searched.  With more than one rank
+    # the gathered result is compared with a single-GPU search of the whole batch on every rank.
     c3 = None
     if "c3" in sections:
         c3_local = None
@@ -581,49 +584,62 @@ def run_b200(args):
             w3 = synthetic.c3_event_batch(seed=0)
             part = event_sharding.partition_events(w3.row_splits, world)
             c3_coords = w3.coords.to(dev)
+            c3_rs = w3.row_splits.to(dev)
 
-            def c3_search():
-                return event_sharding.local_binned_select_knn(w3.K, c3_coords, w3.row_splits, part.events[rank])
+            def c3_run(mode, chunks):
+                if world == 1 or mode == "none":
+                    return event_sharding.local_binned_select_knn(w3.K, c3_coords, w3.row_splits, part.events[rank])
+                return event_sharding.sharded_binned_select_knn(w3.K, c3_coords, w3.row_splits, gather=mode,
+                                                                n_chunks=chunks, check=False)
 
-            for _ in range(2):
-                res = c3_search()
-            del res
-            torch.cuda.synchronize(dev)
-            e0 = torch.cuda.Event(enable_timing=True)
-            e1 = torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(c3_reps):
-                rows, idx3, dsq3 = c3_search()
-            e1.record()
-            torch.cuda.synchronize(dev)
-            c3_local = e0.elapsed_time(e1) / c3_reps
+            def c3_time(mode, chunks):
+                for _ in range(2):
+                    res = c3_run(mode, chunks)
+                del res
+                barrier()
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(c3_reps):
+                    res = c3_run(mode, chunks)
+                e1.record()
+                torch.cuda.synchronize(dev)
+                del res
+                return e0.elapsed_time(e1) / c3_reps
+
+            c3_local = {"none": c3_time("none", 1)}
+            if world > 1:
+                c3_local["all"] = c3_time("all", 3)
+                c3_local["all_one_group"] = c3_time("all", 1)
+                c3_local["root"] = c3_time("root", 3)
+                # correctness of the exchange, on every rank: same distances bit for bit and same
+                # neighbour sets as one GPU searching the whole batch
+                g_idx, g_dsq = c3_run("all", 3)
+                r_idx, r_dsq = fgc.binned_select_knn(w3.K, c3_coords, c3_rs)
+                c3_local["equal"] = bool(torch.equal(torch.sort(g_dsq, 1).values, torch.sort(r_dsq, 1).values)) and \
+                    bool(torch.equal(torch.sort(g_idx, 1).values, torch.sort(r_idx, 1).values))
+                del g_idx, g_dsq, r_idx, r_dsq
         except Exception as exc:          # noqa: BLE001
+            c3_local = None
             print("bench.py: C3 section failed on rank %d: %r" % (rank, exc), file=sys.stderr)
         if all_ranks_ok(c3_local is not None):
-            c3_ms = max_over_ranks(c3_local)
-            c3_gather_ms = 0.0
-            if world > 1:
-                barrier()
-                g0 = torch.cuda.Event(enable_timing=True)
-                g1 = torch.cuda.Event(enable_timing=True)
-                full = event_sharding.gather_rows(rows, [idx3, dsq3], w3.n_points, part.points)   # warm-up
-                del full
-                barrier()
-                g0.record()
-                full = event_sharding.gather_rows(rows, [idx3, dsq3], w3.n_points, part.points)
-                g1.record()
-                barrier()
-                c3_gather_ms = max_over_ranks(g0.elapsed_time(g1))
-                del full
+            c3_ms = max_over_ranks(c3_local["none"])
             c3 = {"config": "c3: 64 events of 50000..150000 uniform points, D=3, K=64, forward, sharded by event "
                             "(greedy longest-processing-time on point counts)",
                   "n_points": w3.n_points, "n_gpus": world, "search_ms": c3_ms,
-                  "points_per_s": w3.n_points / (c3_ms * 1e-3),
-                  "gather_ms": c3_gather_ms, "scaling": "strong",
+                  "points_per_s": w3.n_points / (c3_ms * 1e-3), "scaling": "strong",
                   "largest_shard_points": max(part.points),
-                  "note": "search_ms: local search + local->global ids, max over ranks; gather_ms: padded "
-                          "all_gather of idx and distsq to every rank (NCCL), second call"}
-        rows = idx3 = dsq3 = c3_coords = None
+                  "note": "search_ms: local search + local->global ids, rows stay sharded, max over ranks"}
+            if world > 1:
+                c3["search_and_gather_all_ms"] = max_over_ranks(c3_local["all"])
+                c3["search_and_gather_all_one_group_ms"] = max_over_ranks(c3_local["all_one_group"])
+                c3["search_and_gather_root_ms"] = max_over_ranks(c3_local["root"])
+                c3["gathered_equals_single_gpu"] = all_ranks_ok(c3_local["equal"])
+                c3["gather_note"] = ("search + exchange of idx (int32 on the wire, widened to int64 on receipt) and "
+                                     "distsq, per-event point-to-point blocks (NCCL) into the final tensors; "
+                                     "'all': every rank ends with all rows, three groups of events per rank so that "
+                                     "transfers overlap the search; 'root': rank 0 only")
+        c3_coords = None
 
     # ---- object-condensation index matrices (the loss-side consumer of the same row splits) --
     oc = None

@@ -120,6 +120,10 @@ SIGNATURES = {
                                    c_void_p]),
     "fgc_select_with_default": (ctypes.c_int, [c_void_p, c_i64, c_void_p, c_i64, c_i64, c_i32, c_void_p,
                                                c_void_p, c_void_p]),
+    "fgc_pyg_workspace_bytes": (c_size, [c_i64]),
+    "fgc_row_splits_from_strict_batch": (ctypes.c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_size, c_void_p]),
+    "fgc_pyg_read_count": (ctypes.c_int, [c_void_p, ctypes.POINTER(c_i64), c_void_p]),
+    "fgc_strict_batch_from_row_splits": (ctypes.c_int, [c_void_p, c_i64, c_i64, c_void_p, c_void_p]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

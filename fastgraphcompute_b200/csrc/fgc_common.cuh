@@ -17,6 +17,17 @@
 
 #define FGC_CHECK_LAUNCH() FGC_RETURN_IF_CUDA(cudaGetLastError())
 
+// Bounds checks of the debug build (nvcc -DFGC_DEBUG; fastgraphcompute_b200/build.py --debug
+// writes libfgc_b200_debug.so).  FGC_DBG_OK(cond, status_ptr) is `true` in a normal build.  In
+// the debug build it evaluates cond and, when it does not hold, sets FGC_STATUS_DEBUG_BOUNDS in
+// the status word and yields false, so that the caller skips the access: a bad index is
+// recorded and reported through fgc_read_status instead of becoming a memory fault.
+#ifdef FGC_DEBUG
+#define FGC_DBG_OK(cond, status_ptr) ((cond) ? true : (atomicOr((int *)(status_ptr), FGC_STATUS_DEBUG_BOUNDS), false))
+#else
+#define FGC_DBG_OK(cond, status_ptr) (true)
+#endif
+
 namespace fgc {
 
 // Number of SMs of the current device (148 on a B200), asked once per device and kept.  Grids of

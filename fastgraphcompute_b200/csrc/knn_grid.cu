@@ -308,8 +308,8 @@ k_histogram(const float *__restrict__ coords, int n_vert, int n_coords,
         // the fourth dimension has one cell (b[3] = 0) in a grid over three coordinates
         flat = e * g->B + ((b[0] * g->n[1] + b[1]) * g->n[2] + b[2]) * g->n[3] + b[3];
     }
-    const unsigned active = __ballot_sync(FGC_FULL_MASK, live);
-    if (live) {
+    const unsigned active = __ballot_sync(FGC_FULL_MASK, live && FGC_DBG_OK(flat >= 0 && flat < g->total_bins, &g->status));
+    if (active >> (threadIdx.x & 31) & 1) {
         // warp-aggregated: one atomic per distinct cell in the warp
         const unsigned peers = __match_any_sync(active, flat);
         const int leader = __ffs(peers) - 1;
@@ -329,7 +329,8 @@ k_fill_ids(int n_vert, const KnnGrid *__restrict__ g, const int *__restrict__ bo
 {
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= n_vert || g->status != 0) return;
-    stmp[bounds[pbin[v]] + prank[v]] = v;
+    const int pos = bounds[pbin[v]] + prank[v];
+    if (FGC_DBG_OK(pos >= 0 && pos < n_vert, &g->status)) stmp[pos] = v;
 }
 
 // Everything that is kept per point in cell order: original id, coordinates padded to
@@ -378,7 +379,8 @@ k_rank_place(const float *__restrict__ coords, int n_vert, int n_coords, int nv,
     if (len <= kRankMax) {
         int rank = 0;
         for (int t = 0; t < len; t++) rank += stmp[beg + t] < v ? 1 : 0;
-        place_point(beg + rank, v, bin, coords, n_coords, nv, direction, sorig, scoords, sbin, sflag);
+        if (FGC_DBG_OK(beg >= 0 && rank < len && beg + rank < n_vert, &g->status))
+            place_point(beg + rank, v, bin, coords, n_coords, nv, direction, sorig, scoords, sbin, sflag);
     } else {
         const int r = prank[v];
         sorig[beg + r] = v;
@@ -647,7 +649,12 @@ extern "C" int fgc_knn_read_counters(const void *workspace, uint64_t *counters_h
     cudaStream_t s = (cudaStream_t)stream;
     FGC_RETURN_IF_CUDA(cudaMemcpyAsync(&h, workspace, sizeof(KnnGrid), cudaMemcpyDeviceToHost, s));
     FGC_RETURN_IF_CUDA(cudaStreamSynchronize(s));
-    if (counters_host) for (int i = 0; i < 8; i++) counters_host[i] = h.counters[i];
+    if (counters_host) {
+        for (int i = 0; i < 6; i++) counters_host[i] = h.counters[i];
+        // facts about the grid build (always available, not only after a counting search)
+        counters_host[6] = (uint64_t)h.n_hard;          // queries the last search handed to whole CTAs
+        counters_host[7] = (uint64_t)h.n_huge_cells;    // cells above 512 points (sorted by one CTA each)
+    }
     if (grid_shape_host) { grid_shape_host[0] = h.n[0]; grid_shape_host[1] = h.n[1]; grid_shape_host[2] = h.n[2] * h.n[3]; }
     if (cell_width_host) *cell_width_host = h.w;
     return FGC_OK;

@@ -174,6 +174,7 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
     const int nc = a.n_coords;
     const uint8_t *__restrict__ sflag = a.sflag;
     const int orig_q = __ldg(a.sorig + qi);
+    if (!FGC_DBG_OK(orig_q >= 0 && orig_q < a.n_vert, &g->status)) return;
     int64_t *__restrict__ out_i = a.out_idx + (size_t)orig_q * K;
     float *__restrict__ out_d = a.out_dist + (size_t)orig_q * K;
 
@@ -191,7 +192,7 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
     // one step: lane evaluates the candidate at sorted position j (if act)
     auto process = [&](int j, bool act) {
         float dc = __uint_as_float(kInfBits);
-        if (act) {
+        if (act && FGC_DBG_OK(j >= 0 && j < a.n_vert, &g->status)) {
             float4 c[NV];
 #pragma unroll
             for (int v = 0; v < NV; v++) c[v] = __ldg(a.scoords + (size_t)j * NV + v);
@@ -345,6 +346,9 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
                         if (md > __uint_as_float(list.tau) * 1.00001f) valid = false;
                     }
                     int start = 0, len = 0;
+                    if (valid) {
+                        valid = FGC_DBG_OK(zlo >= 0 && zhi < nl && e >= 0 && e < g->n_events, &g->status);
+                    }
                     if (valid) {
                         const int rowbase = G4 ? e * B + ((g0 * n1 + g1) * n2 + g2) * n3 : e * B + (g0 * n1 + g1) * n2;
                         start = __ldg(a.bounds + rowbase + zlo);

@@ -121,71 +121,202 @@ def local_binned_select_knn(K, coords, row_splits, events, direction=None,
     return rows, replace_fn(idx.contiguous(), rows), dsq
 
 
-def gather_rows(rows, tensors, n_total, points_per_rank, group=None):
-    """All-gather per-rank row blocks into full tensors in global row order, on every rank.
+def chunk_events(events: Sequence[int], row_splits, n_chunks: int) -> List[List[int]]:
+    """Split one rank's (ascending) event list into ``n_chunks`` consecutive groups of about the
+    same number of points; groups may be empty.  A pure function of its arguments, so every rank
+    computes every other rank's groups from the partition table alone."""
+    rs = [int(v) for v in torch.as_tensor(row_splits).cpu().tolist()]
+    n_chunks = max(int(n_chunks), 1)
+    sizes = [rs[e + 1] - rs[e] for e in events]
+    total = sum(sizes)
+    out = [[] for _ in range(n_chunks)]
+    acc = 0
+    for e, sz in zip(events, sizes):
+        # the group in which the event's midpoint falls
+        c = min(n_chunks - 1, int((acc + 0.5 * sz) * n_chunks / total)) if total > 0 else 0
+        out[c].append(e)
+        acc += sz
+    return out
 
-    Contributions differ in length, so each rank pads to the largest shard; the receiver cuts
-    the padding off using the partition table (known on every rank) and checks that it agrees
-    with the sizes the ranks report.
+
+def _agree_or_raise(ok: bool, message: str, device, group=None):
+    """All ranks learn whether every rank is ready to exchange; a rank that is not raises its own
+    message, the others raise a generic one -- before any data moves, so that nobody waits for a
+    peer that has left."""
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    if not ok:
+        raise RuntimeError(message)
+    if int(flag.item()) == 0:
+        raise RuntimeError("another rank's shard disagrees with the partition table; nothing was exchanged")
+
+
+class EventRowExchange:
+    """Moves per-event row blocks of the ranks into full tensors in global row order.
+
+    Events are contiguous row ranges of the batch, so a block is sent from the owner's local
+    result straight into rows [row_splits[e], row_splits[e+1]) of the receiver's full tensor: no
+    padding, no staging buffer, no re-ordering pass.  One grouped set of point-to-point transfers
+    per call of ``post`` (NCCL over NVLink for CUDA tensors, gloo on CPU); the transfers of one
+    group of events can run while the next group is still being searched.
+
+    mode "all": every rank receives every block; "root": only ``root`` does.
     """
+
+    def __init__(self, row_splits, part: EventPartition, templates, mode="all", root=0, group=None):
+        if mode not in ("all", "root"):
+            raise ValueError("mode must be 'all' or 'root'")
+        self.rs = [int(v) for v in torch.as_tensor(row_splits).cpu().tolist()]
+        self.part = part
+        self.mode = mode
+        self.root = root
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.receives = mode == "all" or self.rank == root
+        n_total = self.rs[-1]
+        # templates: (dtype, trailing shape, device) per exchanged tensor
+        self.full = [torch.empty((n_total,) + tuple(shape), dtype=dtype, device=device) if self.receives else None
+                     for dtype, shape, device in templates]
+        self.pending = []
+        self.keep = []
+        self.comm_stream = None
+        dev = templates[0][2]
+        if torch.device(dev).type == "cuda":
+            self.comm_stream = torch.cuda.Stream(device=dev)
+
+    def _global_rank(self, r):
+        return r if self.group is None else dist.get_global_rank(self.group, r)
+
+    def post(self, my_events: Sequence[int], blocks, events_of_rank):
+        """Start the transfers of one group: ``blocks`` are this rank's tensors for ``my_events``
+        (rows concatenated event by event), ``events_of_rank[r]`` the events rank r contributes
+        in this group.  Returns at once; ``finish`` waits."""
+        sizes = [self.rs[e + 1] - self.rs[e] for e in my_events]
+        n_local = sum(sizes)
+        for b in blocks:
+            if b.shape[0] != n_local:
+                raise RuntimeError("shard of rank %d has %d rows, the partition table says %d"
+                                   % (self.rank, b.shape[0], n_local))
+        ops = []
+        peers = [p for p in range(self.world) if p != self.rank]
+        # own rows: a device copy per event
+        if self.receives:
+            off = 0
+            for e, sz in zip(my_events, sizes):
+                for full, b in zip(self.full, blocks):
+                    full[self.rs[e]: self.rs[e] + sz].copy_(b[off: off + sz], non_blocking=True)
+                off += sz
+        for p in peers:
+            if self.mode == "all" or p == self.root:
+                off = 0
+                for e, sz in zip(my_events, sizes):
+                    if sz:
+                        for b in blocks:
+                            ops.append(dist.P2POp(dist.isend, b[off: off + sz], self._global_rank(p), self.group))
+                    off += sz
+            if self.receives:
+                for e in events_of_rank[p]:
+                    sz = self.rs[e + 1] - self.rs[e]
+                    if sz:
+                        for full in self.full:
+                            ops.append(dist.P2POp(dist.irecv, full[self.rs[e]: self.rs[e] + sz],
+                                                  self._global_rank(p), self.group))
+        self.keep.append(blocks)
+        if not ops:
+            return
+        if self.comm_stream is not None:
+            # issue from a side stream that waits for the producer of the blocks: the launching
+            # stream is free to start the next group's search while these transfers run
+            self.comm_stream.wait_stream(torch.cuda.current_stream(self.comm_stream.device))
+            with torch.cuda.stream(self.comm_stream):
+                self.pending.extend(dist.batch_isend_irecv(ops))
+        else:
+            self.pending.extend(dist.batch_isend_irecv(ops))
+
+    def finish(self):
+        """Wait for every posted transfer; returns the full tensors (None on a rank that does not
+        receive)."""
+        if self.comm_stream is not None:
+            with torch.cuda.stream(self.comm_stream):
+                for w in self.pending:
+                    w.wait()
+            torch.cuda.current_stream(self.comm_stream.device).wait_stream(self.comm_stream)
+        else:
+            for w in self.pending:
+                w.wait()
+        self.pending = []
+        self.keep = []
+        return self.full
+
+
+def gather_rows(rows, tensors, n_total, points_per_rank, group=None, row_splits=None, part=None,
+                mode="all", root=0):
+    """Bring per-rank row blocks (rows of the rank's events, event by event) together as full
+    tensors in global row order: on every rank (mode "all") or on ``root`` only (mode "root",
+    other ranks get None).  The ranks first agree that every shard has the size the partition
+    table says (one 4-byte all-reduce and a host read); a rank whose shard differs raises, and so
+    do the others, before any row moves."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     n_local = rows.shape[0]
-    if n_local != points_per_rank[rank]:
-        raise RuntimeError("shard of rank %d has %d rows, the partition table says %d"
-                           % (rank, n_local, points_per_rank[rank]))
-    sizes = torch.tensor([n_local], dtype=torch.int64, device=rows.device)
-    all_sizes = [torch.zeros_like(sizes) for _ in range(world)]
-    dist.all_gather(all_sizes, sizes, group=group)
-    all_sizes = [int(s.item()) for s in all_sizes]
-    if all_sizes != list(points_per_rank):
-        raise RuntimeError("ranks disagree with the partition table: %s vs %s" % (all_sizes, list(points_per_rank)))
-    if sum(all_sizes) != n_total:
-        raise RuntimeError("shards do not cover the batch: %d rows of %d" % (sum(all_sizes), n_total))
-    n_max = max(all_sizes) if all_sizes else 0
-
-    def pad(t):
-        if t.shape[0] == n_max:
-            return t.contiguous()
-        p = torch.zeros((n_max,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
-        p[: t.shape[0]] = t
-        return p
-
-    # one receive buffer per tensor ([world * n_max, ...], rank r's block at r * n_max): a single
-    # collective each, no per-rank staging copies
-    rows_all = torch.empty((world * n_max,), dtype=rows.dtype, device=rows.device)
-    dist.all_gather_into_tensor(rows_all, pad(rows), group=group)
-    outs = []
-    for t in tensors:
-        buf = torch.empty((world * n_max,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
-        dist.all_gather_into_tensor(buf, pad(t), group=group)
-        full = torch.empty((n_total,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
-        for r in range(world):
-            lo = r * n_max
-            full.index_copy_(0, rows_all[lo: lo + all_sizes[r]], buf[lo: lo + all_sizes[r]])
-        outs.append(full)
-    return outs
+    ok = n_local == points_per_rank[rank] and sum(points_per_rank) == n_total
+    _agree_or_raise(ok, "shard of rank %d has %d rows, the partition table says %d (batch: %d rows, table: %d)"
+                    % (rank, n_local, points_per_rank[rank], n_total, sum(points_per_rank)), rows.device, group)
+    if row_splits is None or part is None:
+        raise ValueError("gather_rows needs the row splits and the partition table")
+    ex = EventRowExchange(row_splits, part, [(t.dtype, t.shape[1:], t.device) for t in tensors], mode, root, group)
+    ex.post(part.events[rank], [t.contiguous() for t in tensors], part.events)
+    return ex.finish()
 
 
 def sharded_binned_select_knn(K, coords, row_splits, direction=None, torch_compatible_indices=False,
                               group=None, gather=True, knn_fn: Optional[Callable] = None,
-                              replace_fn: Optional[Callable] = None):
+                              replace_fn: Optional[Callable] = None, root=0, n_chunks=1, check=True):
     """binned_select_knn over a batch that every rank holds, each rank searching its own events.
 
-    Returns (idx, distsq) for the whole batch on every rank (gather=True), or this rank's
-    (global_rows, idx, distsq) block without any collective (gather=False).  Forward only.
+    gather = True / "all": (idx, distsq) of the whole batch on every rank; "root": on ``root``
+    only (None, None elsewhere); False / "none": this rank's (global_rows, idx, distsq) block
+    without any collective.  Forward only.
+
+    Neighbour ids travel as int32 (row counts are below 2^31) and are widened to the public int64
+    on receipt: a third fewer bytes on the links.  With n_chunks > 1 a rank searches its events
+    in that many groups and the rows of a finished group travel while the next one is searched.
+    check=False skips the agreement step (a 4-byte all-reduce and a host read).
     """
     if not dist.is_initialized():
         raise RuntimeError("torch.distributed is not initialised")
+    mode = {True: "all", False: "none"}.get(gather, gather)
+    if mode not in ("all", "root", "none"):
+        raise ValueError("gather must be True/'all', 'root' or False/'none'")
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     part = partition_events(row_splits, world)
-    rows, idx, dsq = local_binned_select_knn(K, coords, row_splits, part.events[rank], direction,
-                                             torch_compatible_indices, knn_fn, replace_fn)
-    if not gather:
-        return rows, idx, dsq
-    full_idx, full_dsq = gather_rows(rows, [idx, dsq], coords.shape[0], part.points, group)
-    return full_idx, full_dsq
+    if mode == "none":
+        return local_binned_select_knn(K, coords, row_splits, part.events[rank], direction,
+                                       torch_compatible_indices, knn_fn, replace_fn)
+    if check:
+        n_total = int(torch.as_tensor(row_splits)[-1])
+        _agree_or_raise(sum(part.points) == n_total == coords.shape[0],
+                        "rank %d: the partition table covers %d rows, the batch has %d"
+                        % (rank, sum(part.points), coords.shape[0]), coords.device, group)
+    chunks = [chunk_events(part.events[r], row_splits, n_chunks) for r in range(world)]
+    ex = EventRowExchange(row_splits, part, [(torch.int32, (K,), coords.device), (torch.float32, (K,), coords.device)],
+                          mode, root, group)
+    for c in range(max(int(n_chunks), 1)):
+        mine = chunks[rank][c]
+        if mine:
+            rows, idx, dsq = local_binned_select_knn(K, coords, row_splits, mine, direction,
+                                                     torch_compatible_indices, knn_fn, replace_fn)
+            blocks = [idx.to(torch.int32), dsq.contiguous()]
+        else:
+            blocks = [torch.empty((0, K), dtype=torch.int32, device=coords.device),
+                      torch.empty((0, K), dtype=torch.float32, device=coords.device)]
+        ex.post(mine, blocks, [chunks[r][c] for r in range(world)])
+    full_idx32, full_dsq = ex.finish()
+    if full_idx32 is None:
+        return None, None
+    return full_idx32.to(torch.int64), full_dsq
 
 
 def allreduce_gradients(parameters, group=None):

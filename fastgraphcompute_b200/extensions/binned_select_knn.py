@@ -254,7 +254,7 @@ def binned_select_knn_with_order(K: int, coords: torch.Tensor, row_splits: torch
         idx, dist, order = torch.ops.fgc_b200.knn_forward(coords, row_splits, K, dirn, torch_compatible_indices)
         return idx, dist, order
     else:
-        if torch.jit.is_tracing():
+        if torch.jit.is_tracing() or torch.compiler.is_compiling():
             return torch.ops.fgc_b200.knn_forward(coords, row_splits, K, dirn, torch_compatible_indices)
         return _BinnedKNN.apply(coords, row_splits, K, dirn, torch_compatible_indices)
 

@@ -46,7 +46,10 @@ def gravnet_aggregate(propagate: torch.Tensor, neighbor_idx: torch.Tensor, dists
         fmean, fmax, _ = torch.ops.fgc_b200.gravnet_aggregate(propagate, neighbor_idx, distsq, order)
         return fmean, fmax
     else:
-        if torch.jit.is_tracing():
+        if torch.jit.is_tracing() or torch.compiler.is_compiling():
+            # graph capture (jit.trace, torch.compile) goes through the dispatcher op, which has
+            # shape inference and autograd registered; the eager node below talks to the
+            # library directly
             fmean, fmax, _ = torch.ops.fgc_b200.gravnet_aggregate(propagate, neighbor_idx, distsq, order)
             return fmean, fmax
         return _GravNetAggregate.apply(propagate, neighbor_idx, distsq, order)

@@ -219,16 +219,30 @@ def bin_by_coordinates(coordinates: Tensor, row_splits: Tensor, bin_width: Optio
 _REFERENCE_LIBS = []
 
 
+def reference_ops_loaded() -> bool:
+    """True when some other library (the reference's binned_knn_ops.so) has already defined the
+    reference's op names in this process."""
+    try:
+        torch.ops.fastgraphcompute_custom_ops.binned_select_knn_autograd
+        return not _REFERENCE_LIBS
+    except (AttributeError, RuntimeError):
+        return False
+
+
 def register_reference_op_names():
     """Publish the ops under the names the reference registers, so that scripted code written
     against ``torch.ops.fastgraphcompute_custom_ops.binned_select_knn_autograd``,
     ``torch.ops.bin_by_coordinates.bin_by_coordinates``,
+    ``torch.ops.binned_select_knn.binned_select_knn`` (the search on caller-binned input),
     ``torch.ops.binned_select_knn_grad.binned_select_knn_grad`` and
     ``torch.ops.index_replacer.index_replacer`` resolves to this implementation.  Call it
     instead of loading the reference's binned_knn_ops.so (both in one process would define the
-    same schemas twice).  Returns the list of namespaces it registered."""
+    same schemas twice; when that library is already loaded nothing is registered).  Returns the
+    list of namespaces it registered."""
     if _REFERENCE_LIBS:
         return [l.ns for l in _REFERENCE_LIBS]
+    if reference_ops_loaded():
+        return []
 
     def knn_autograd(coords, row_splits, K, direction, n_bins, max_bin_dims, torch_compatible_indices):
         idx, dist, _ = torch.ops.fgc_b200.knn_forward(coords, row_splits, K, direction,
@@ -237,6 +251,22 @@ def register_reference_op_names():
 
     def knn_grad(grad_distances, indices, distances, coordinates):
         return torch.ops.fgc_b200.knn_backward(grad_distances, indices, coordinates)
+
+    def knn_on_binned_input(coordinates, bin_idx, dim_bin_idx, bin_boundaries, n_bins, bin_width, direction,
+                            tf_compat, use_direction, K):
+        # The reference's low-level search (extensions/binned_select_knn.cpp:82-91) takes points
+        # that the caller has already binned and sorted by bin, and answers with indices into
+        # that sorted order.  The caller's bins say where its row splits are (every row split
+        # owns prod(n_bins) consecutive bins) and nothing else matters for the result, so the
+        # search runs on this library's own grid inside those row splits.
+        per_split = int(torch.prod(n_bins.to(torch.int64)).item())
+        n_b = bin_boundaries.shape[0] - 1
+        if per_split < 1 or n_b % per_split != 0:
+            raise RuntimeError("binned_select_knn: bin_boundaries do not hold a whole number of row splits")
+        row_splits = bin_boundaries.to(torch.int64)[::per_split].contiguous()
+        idx, dist, _ = torch.ops.fgc_b200.knn_forward(coordinates, row_splits, K,
+                                                      direction if use_direction else None, tf_compat)
+        return idx, dist
 
     specs = [
         ("fastgraphcompute_custom_ops",
@@ -250,6 +280,11 @@ def register_reference_op_names():
         ("binned_select_knn_grad",
          "binned_select_knn_grad(Tensor grad_distances, Tensor indices, Tensor distances, Tensor coordinates) -> Tensor",
          "binned_select_knn_grad", knn_grad, "CompositeImplicitAutograd"),
+        ("binned_select_knn",
+         "binned_select_knn(Tensor coordinates, Tensor bin_idx, Tensor dim_bin_idx, Tensor bin_boundaries, "
+         "Tensor n_bins, Tensor bin_width, Tensor direction, bool tf_compat, bool use_direction, int K) "
+         "-> (Tensor, Tensor)",
+         "binned_select_knn", knn_on_binned_input, "CompositeImplicitAutograd"),
         ("index_replacer",
          "index_replacer(Tensor to_be_replaced, Tensor replacements) -> Tensor",
          "index_replacer", lambda a, b: torch.ops.fgc_b200.index_replacer(a, b), "CompositeImplicitAutograd"),

@@ -49,6 +49,7 @@ extern "C" {
 #define FGC_STATUS_BAD_NBINS 8      /* binning: some n_bins <= 0 */
 #define FGC_STATUS_BAD_BINWIDTH 16  /* binning: bin_width <= 0 */
 #define FGC_STATUS_INTERNAL 32      /* an internal consistency check failed */
+#define FGC_STATUS_DEBUG_BOUNDS 64  /* only in a library built with -DFGC_DEBUG: an index was out of range (the access was skipped) */
 
 #define FGC_MAX_K 257               /* self + 256 neighbours */
 #define FGC_MAX_BIN_DIMS 8          /* coordinate dimensions accepted by fgc_bin_* */
@@ -197,8 +198,10 @@ int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
  * Diagnostics of a workspace, copied to the host (synchronises the stream): eight 64-bit
  * counters that a search launched with FGC_SEARCH_COUNT accumulates ([0] distance
  * evaluations, [1] 32-candidate steps, [2] list insertions, [3] metadata batches, [4] shells,
- * [5] queries that scanned their whole row split, [6] and [7] unused), the grid shape [3] and
- * the cell width.
+ * [5] queries that scanned their whole row split), two facts that need no counting search
+ * ([6] queries the last search handed to whole CTAs because their walk gave up in a row split
+ * of more than 4096 points, [7] cells of more than 512 points), the grid shape [3] and the
+ * cell width.
  * Any output pointer may be NULL.  No counterpart in the reference.
  */
 int fgc_knn_read_counters(const void *workspace, uint64_t *counters_host,
@@ -400,6 +403,27 @@ int fgc_oc_fill(const void *workspace, size_t workspace_bytes, int64_t n_vert, c
 int fgc_select_with_default(const int64_t *idx, int64_t n_idx, const void *feat, int64_t n_rows_feat,
                             int64_t n_feat, int32_t word_bytes, const void *default_word_host,
                             void *out, fgc_stream_t stream);
+
+/*
+ * Conversions between row splits and PyTorch-Geometric style batch vectors on the device
+ * (fastgraphcompute/torch_geometric_interface.py:4-42 row_splits_from_strict_batch and :45-74
+ * strict_batch_from_row_splits of the reference, which use nonzero / repeat_interleave).
+ *
+ * fgc_row_splits_from_strict_batch: batch[n_points] int64, the points of one row split
+ * contiguous -> out_row_splits (room for n_points + 1 entries; only the first *count are
+ * written): 0, every position whose id differs from its predecessor's, n_points.  The count
+ * stays in the workspace (fgc_pyg_workspace_bytes(n_points) bytes) until fgc_pyg_read_count
+ * copies it to the host (synchronises the stream).  An empty batch gives [0, 0].
+ *
+ * fgc_strict_batch_from_row_splits: out_batch[i] = index of the row split that holds point i,
+ * for i < n_points (= row_splits[n_rs - 1], which the caller knows or reads).
+ */
+size_t fgc_pyg_workspace_bytes(int64_t n_points);
+int fgc_row_splits_from_strict_batch(const int64_t *batch, int64_t n_points, int64_t *out_row_splits,
+                                     void *workspace, size_t workspace_bytes, fgc_stream_t stream);
+int fgc_pyg_read_count(const void *workspace, int64_t *n_row_splits_host, fgc_stream_t stream);
+int fgc_strict_batch_from_row_splits(const int64_t *row_splits, int64_t n_rs, int64_t n_points,
+                                     int64_t *out_batch, fgc_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -3,8 +3,8 @@
     python oracle/build_ref.py && python tests/golden/make_golden.py
 
 Needs oracle/_ref/binned_knn_ops.so (built from the unmodified reference
-sources).  Writes tests/golden/{knn,binning,gravnet,misc,stacked,oc,select}.npz
-(`python make_golden.py stacked` / `oc` / `select` write only that file).  The tests only
+sources).  Writes tests/golden/{knn,binning,gravnet,misc,stacked,oc,select,pyg}.npz
+(`python make_golden.py stacked` / `oc` / `select` / `pyg` write only that file).  The tests only
 read those files; they never need the reference checkout.
 """
 import os
@@ -49,6 +49,45 @@ def run_knn(c):
 
 STACKED = dict(n=700, row_splits=[0, 300, 700], in_dim=16, prop_dim=8, space_dim=3, k=10, hidden_dim=32,
                output_dim=5, num_gravnet_layers=2)
+
+
+def make_pyg():
+    """row_splits <-> batch conversions recorded from the reference's own functions
+    (fastgraphcompute/torch_geometric_interface.py, loaded from its file: the module is plain
+    tensor code).  Inputs: the shapes its unit tests use (three events, one event, no points,
+    one point per event) and seeded random event sizes with empty events and non-consecutive
+    ids."""
+    import importlib.util
+    path = os.path.join(build_ref.default_reference_root(), "fastgraphcompute", "torch_geometric_interface.py")
+    spec = importlib.util.spec_from_file_location("ref_pyg_interface", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    rng = np.random.RandomState(7)
+    batches = {
+        "three_events": np.array([0, 0, 0, 1, 1, 2, 2, 2]),
+        "one_event": np.zeros(4, np.int64),
+        "no_points": np.zeros(0, np.int64),
+        "one_point_each": np.arange(4),
+        "ids_with_gaps": np.repeat(np.array([3, 4, 9, 10, 40]), [5, 1, 7, 2, 3]),
+        "random_5000": np.repeat(np.arange(300) * 2, rng.randint(1, 40, size=300)),
+    }
+    splits = {
+        "three_events": np.array([0, 3, 5, 8]),
+        "one_event": np.array([0, 4]),
+        "no_points": np.array([0, 0]),
+        "one_point_each": np.arange(5),
+        "with_empty_events": np.array([0, 0, 4, 4, 4, 9, 9]),
+        "random_sizes": np.concatenate([[0], np.cumsum(rng.randint(0, 50, size=400))]),
+    }
+    store = {}
+    for name, b in batches.items():
+        store["batch_to_rs/%s/in" % name] = b.astype(np.int64)
+        store["batch_to_rs/%s/out" % name] = ref.row_splits_from_strict_batch(torch.tensor(b, dtype=torch.int64)).numpy()
+    for name, r in splits.items():
+        store["rs_to_batch/%s/in" % name] = r.astype(np.int64)
+        store["rs_to_batch/%s/out" % name] = ref.strict_batch_from_row_splits(torch.tensor(r, dtype=torch.int64)).numpy()
+    np.savez_compressed(os.path.join(HERE, "pyg.npz"), **store)
+    print("pyg done:", len(batches), "+", len(splits), "cases")
 
 
 def make_stacked():
@@ -144,6 +183,9 @@ def main():
     if "oc" in sys.argv[1:]:
         make_oc()
         return
+    if "pyg" in sys.argv[1:]:
+        make_pyg()
+        return
     store = {}
     for name, c in cases.knn_cases().items():
         out = run_knn(c)
@@ -222,6 +264,7 @@ def main():
     make_stacked()
     make_oc()
     make_select()
+    make_pyg()
 
 
 if __name__ == "__main__":

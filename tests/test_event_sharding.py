@@ -43,6 +43,15 @@ def test_shard_rows():
     assert rows.numel() == 0 and local.tolist() == [0]
 
 
+def test_chunk_events():
+    rs = [0, 10, 10, 40, 45, 100]
+    assert es.chunk_events([0, 1, 2, 3, 4], rs, 1) == [[0, 1, 2, 3, 4]]
+    c = es.chunk_events([0, 2, 4], rs, 2)
+    assert sorted(e for g in c for e in g) == [0, 2, 4] and len(c) == 2
+    assert es.chunk_events([], rs, 3) == [[], [], []]
+    assert es.chunk_events([1], rs, 2) == [[1], []]          # an empty event lands in the first group
+
+
 def _cpu_knn(K, coords, row_splits, direction=None, torch_compatible_indices=False):
     from oracle import oracle
     idx, d = oracle.binned_select_knn(K, coords.numpy(), row_splits.numpy(),
@@ -54,6 +63,23 @@ def _cpu_knn(K, coords, row_splits, direction=None, torch_compatible_indices=Fal
 def _cpu_replace(idx, table):
     from oracle import oracle
     return torch.from_numpy(oracle.index_replacer(idx.numpy(), table.numpy()))
+
+
+def _join_all(procs, limit):
+    """Join the workers; whoever is still alive after the limit is terminated (then killed)
+    before anything is asserted, so that a stuck rank never outlives the test."""
+    try:
+        for p in procs:
+            p.join(limit)
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
+                    p.join(10)
+    assert [p.exitcode for p in procs] == [0] * len(procs)
 
 
 def _free_port():
@@ -82,6 +108,18 @@ def _worker(rank, world, port, fail_rank, out):
             rows, lidx, _ = es.sharded_binned_select_knn(9, coords, rs, gather=False, knn_fn=_cpu_knn,
                                                          replace_fn=_cpu_replace)
             assert torch.equal(lidx[:, 0], rows)
+            # the same in two groups per rank (rows of group 1 travel while group 2 is searched)
+            idx2, dsq2 = es.sharded_binned_select_knn(9, coords, rs, n_chunks=2, knn_fn=_cpu_knn,
+                                                      replace_fn=_cpu_replace)
+            assert idx2.dtype == torch.int64
+            parity.assert_knn_parity(idx2.numpy(), dsq2.numpy(), ref_idx.numpy(), ref_d.numpy())
+            # and gathered on rank 1 only
+            ridx, rdsq = es.sharded_binned_select_knn(9, coords, rs, gather="root", root=1, knn_fn=_cpu_knn,
+                                                      replace_fn=_cpu_replace)
+            if rank == 1:
+                parity.assert_knn_parity(ridx.numpy(), rdsq.numpy(), ref_idx.numpy(), ref_d.numpy())
+            else:
+                assert ridx is None and rdsq is None
             out[rank] = "ok"
         else:
             # a rank whose shard disagrees with the partition table must be detected on the host
@@ -91,7 +129,7 @@ def _worker(rank, world, port, fail_rank, out):
             if rank == fail_rank:
                 rows, idx, dsq = rows[:-1], idx[:-1], dsq[:-1]
             try:
-                es.gather_rows(rows, [idx, dsq], 1000, part.points)
+                es.gather_rows(rows, [idx, dsq], 1000, part.points, row_splits=rs, part=part)
                 out[rank] = "no error"
             except RuntimeError as e:
                 out[rank] = "raised: " + str(e)[:40]
@@ -109,9 +147,7 @@ def test_two_rank_gloo(fail_rank):
     procs = [ctx.Process(target=_worker, args=(r, world, port, fail_rank, out)) for r in range(world)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(120)
-        assert p.exitcode == 0
+    _join_all(procs, 120)
     if fail_rank is None:
         assert dict(out) == {0: "ok", 1: "ok"}
     else:
@@ -153,7 +189,5 @@ def test_allreduce_gradients_two_rank_gloo():
     procs = [ctx.Process(target=_grad_worker, args=(r, world, port, out)) for r in range(world)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(120)
-        assert p.exitcode == 0
+    _join_all(procs, 120)
     assert dict(out) == {0: "ok", 1: "ok"}

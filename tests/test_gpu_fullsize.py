@@ -151,3 +151,101 @@ def test_c4_full_gravnet_event_independence_and_reference_aggregate():
     parity.assert_grad_close(fmax.detach().cpu().numpy(), rmax.detach().cpu().numpy(), 1e-5, "max")
     parity.assert_grad_close(ga[0].cpu().numpy(), gr[0].cpu().numpy(), 1e-5, "d_prop")
     parity.assert_grad_close(ga[1].cpu().numpy(), gr[1].cpu().numpy(), 1e-5, "d_distsq")
+
+
+# ---- at-size comparisons with the CPU oracle / the reference's own ops -------------------------
+
+def _knn_vs_oracle(coords, rs, K, what):
+    idx, dist = fgc.binned_select_knn(K, coords.to(DEV), rs.to(DEV))
+    oidx, odist = oracle.binned_select_knn(K, coords.numpy(), rs.numpy())
+    st = parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), oidx, odist, what=what)
+    assert st["max_rel"] == 0.0, what + ": squared distances must be bit-identical"
+    return st
+
+
+def test_c3_full_event_and_batch_vs_oracle():
+    """C3 at real event size: one event of 100 000 uniform points with K = 64 (the shell walk with
+    two list slots per lane; the scaled-down C3 of the parity file mostly scans whole events), and
+    all 64 events at 5 % size as one batch (int32 row splits, events of 2 500..7 500 points)."""
+    g = torch.Generator().manual_seed(3)
+    _knn_vs_oracle(torch.rand((100000, 3), generator=g), torch.tensor([0, 100000], dtype=torch.int32), 64,
+                   "c3 one full event")
+    w = synthetic.c3_event_batch(scale=0.05)
+    assert w.row_splits.numel() == 65 and w.n_points > 250000
+    _knn_vs_oracle(w.coords, w.row_splits, w.K, "c3 64 events at 5 %")
+
+
+def test_c5_quarter_million_point_event_vs_oracle():
+    """One C5 event of 250 000 points (200 Pareto-sized clusters + uniform background, K = 128),
+    plus a few stray points far away, against the oracle.  The case must reach the parts the small cases do not: cells of more than
+    512 points (sorted by a whole CTA), background queries that give up their walk and are
+    searched by a whole CTA (k_knn_hard), and the four-slots-per-lane list."""
+    import importlib
+    km = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
+    w = synthetic.c5_skewed(scale=0.25, n_events=1)
+    assert w.n_points == 250000 and w.K == 128
+    # forty stray points far outside the unit cube: their walks cross empty space and give up
+    g = torch.Generator().manual_seed(5)
+    stray = 60.0 * torch.rand((40, 3), generator=g) - 30.0
+    coords = torch.cat([w.coords, stray])[torch.randperm(250040, generator=g)].contiguous()
+    row_splits = torch.tensor([0, 250040], dtype=torch.int64)
+    c = coords.to(DEV)
+    rs = row_splits.to(DEV)
+    idx, dist, ws = km.knn_forward_raw(c, rs, w.K, None, False, count_evals=True)
+    counters, shape, width = km.read_counters(ws)
+    assert counters[7] > 0, "no cell above 512 points"
+    assert counters[6] > 0, "no query was handed to k_knn_hard"
+    oidx, odist = oracle.binned_select_knn(w.K, coords.numpy(), row_splits.numpy())
+    st = parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), oidx, odist, what="c5 250k event")
+    assert st["max_rel"] == 0.0
+
+
+def test_c4_full_event_gravnet_vs_reference_module():
+    """One full C4 event (100 000 points, 64 features, k = 40) through GravNetOp forward and
+    backward against the reference module on the CPU (its own kNN, gradient and tensor ops).
+
+    Two comparisons.  (1) Whole module: outputs and gradients to 2e-5 of their scale (the dense
+    layers run on different hardware, so the learned coordinates differ in the last bits and a few
+    near-tied neighbours swap).  (2) Exact: the reference kNN and aggregation fed with THIS
+    module's learned coordinates and propagated features must give the same neighbour sets under
+    the parity rule, bit-identical squared distances, and aggregates within 1e-6."""
+    from oracle import ref_ops
+    if not ref_ops.available():
+        pytest.skip("the reference's CPU ops are not built (oracle/_ref)")
+    gw = synthetic.c4_gravnet(n_events=1)
+    assert gw.x.shape == (100000, 64)
+    ref = synthetic.init_gravnet_weights(
+        ref_ops.RefGravNetOp(gw.in_channels, gw.out_channels, gw.space_dimensions, gw.propagate_dimensions, gw.k))
+    m = GravNetOp(gw.in_channels, gw.out_channels, gw.space_dimensions, gw.propagate_dimensions, gw.k).to(DEV)
+    m.load_state_dict(ref.state_dict())
+    x = gw.x.to(DEV).requires_grad_(True)
+    out, idx, dsq, space = m(x, gw.row_splits.to(DEV))
+    (out ** 2).sum().backward()
+
+    xr = gw.x.clone().requires_grad_(True)
+    rout, ridx, rdsq, rspace = ref(xr, gw.row_splits)
+    (rout ** 2).sum().backward()
+
+    np.testing.assert_allclose(space.detach().cpu().numpy(), rspace.detach().numpy(), rtol=1e-5, atol=2e-6)
+    mine = np.sort(idx.cpu().numpy(), 1)
+    theirs = np.sort(ridx.numpy().astype(np.int64), 1)
+    assert (mine == theirs).mean() > 0.999
+    parity.assert_grad_close(out.detach().cpu().numpy(), rout.detach().numpy(), 2e-5, "c4 out")
+    parity.assert_grad_close(x.grad.cpu().numpy(), xr.grad.numpy(), 2e-5, "c4 grad_x")
+    rgrads = dict(ref.named_parameters())
+    for k, p in m.named_parameters():
+        wk = k.replace(".bias", ".weight")
+        scale = float(np.sqrt(np.mean(rgrads[wk].grad.numpy().astype(np.float64) ** 2)))
+        parity.assert_grad_close(p.grad.cpu().numpy(), rgrads[k].grad.numpy(), 5e-5, "c4 grad " + k, scale=scale)
+
+    # (2) the reference ops on this module's own learned coordinates
+    sp = space.detach().cpu().contiguous()
+    prop = m.propagate_transformations(x).detach().cpu()
+    eidx, edsq = ref_ops.ref_binned_select_knn(gw.k, sp, gw.row_splits)
+    st = parity.assert_knn_parity(idx.cpu().numpy(), dsq.detach().cpu().numpy(), eidx.numpy(), edsq.numpy(),
+                                  what="c4 kNN on learned coordinates")
+    assert st["max_rel"] == 0.0
+    emean, emax = ref_ops.ref_gravnet_aggregate(prop, idx.cpu(), dsq.detach().cpu())
+    fmean, fmax = gravnet_aggregate(prop.to(DEV), idx, dsq.detach())
+    np.testing.assert_allclose(fmean.cpu().numpy(), emean.numpy(), rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(fmax.cpu().numpy(), emax.numpy(), rtol=1e-6, atol=1e-7)

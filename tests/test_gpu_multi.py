@@ -32,7 +32,7 @@ def _worker(rank, world, port, out):
         from fastgraphcompute_b200 import synthetic, event_sharding as es
         w = synthetic.c3_event_batch(scale=0.05, n_events=12)
         coords, rs = w.coords.to(dev), w.row_splits.to(dev)
-        idx, dsq = es.sharded_binned_select_knn(w.K, coords, rs)
+        idx, dsq = es.sharded_binned_select_knn(w.K, coords, rs, n_chunks=2)
         ref_idx, ref_dsq = fgc.binned_select_knn(w.K, coords, rs)
         # distances are bit-identical; the neighbour sets too (slot order may differ because a
         # shard builds its own grid)
@@ -72,7 +72,18 @@ def test_two_gpu_sharded_knn_matches_single_gpu():
     procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(300)
-        assert p.exitcode == 0
+    try:
+        for p in procs:
+            p.join(300)
+    finally:
+        # a rank that is still alive (stuck in a collective after its peer failed, say) must not
+        # outlive the test with a GPU in its hands
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
+                    p.join(10)
+    assert [p.exitcode for p in procs] == [0] * world
     assert dict(out) == {0: "ok", 1: "ok"}

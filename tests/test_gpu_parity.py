@@ -308,6 +308,43 @@ def test_knn_gradient_on_reference_slot_order(golden_dir):
         parity.assert_grad_close(out.cpu().numpy(), c["out"]["grad_coords"], what=name)
 
 
+def test_knn_repeated_search_on_one_grid():
+    """The build/search split: one grid, searched three times.  Clustered points with far
+    outliers in a row split of more than 4096 points make some walks give up, so every search
+    fills the list of queries for k_knn_hard; the list must start empty each time (same rows,
+    same list length, the workspace's cell order untouched) -- and the rows must be right."""
+    from fastgraphcompute_b200 import _cabi
+    import importlib
+    km = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
+    g = torch.Generator().manual_seed(17)
+    n_in, n_out, K = 12000, 60, 20
+    pts = torch.cat([0.5 + 0.002 * torch.randn((n_in, 3), generator=g),
+                     200.0 * torch.rand((n_out, 3), generator=g) - 100.0])
+    pts = pts[torch.randperm(pts.shape[0], generator=g)].contiguous()
+    n = pts.shape[0]
+    rs = torch.tensor([0, n], dtype=torch.int64, device=DEV)
+    c = pts.to(DEV)
+    nb = _cabi.lib.fgc_knn_workspace_bytes(n, 3, 2, K)
+    ws = torch.empty(nb, dtype=torch.uint8, device=DEV)
+    stream = _cabi.current_stream(c.device)
+    assert _cabi.lib.fgc_knn_build_grid(_cabi.ptr(c), n, 3, _cabi.ptr(rs), 2, K, None, 0.0, _cabi.ptr(ws), nb, stream) == 0
+    order0 = km.cell_order(ws, n, 3, 2, K).clone()
+    results, hard = [], []
+    for _ in range(3):
+        idx = torch.full((n, K), -9, dtype=torch.int64, device=DEV)
+        dsq = torch.full((n, K), -9.0, dtype=torch.float32, device=DEV)
+        assert _cabi.lib.fgc_knn_search(n, 3, 2, K, 0, 0, 0, _cabi.ptr(idx), _cabi.ptr(dsq), _cabi.ptr(ws), nb, stream) == 0
+        counters, _, _ = km.read_counters(ws)
+        hard.append(counters[6])
+        results.append((idx, dsq))
+    assert hard[0] > 0 and hard == [hard[0]] * 3, hard
+    assert torch.equal(km.cell_order(ws, n, 3, 2, K), order0)
+    for idx, dsq in results[1:]:
+        assert torch.equal(idx, results[0][0]) and torch.equal(dsq, results[0][1])
+    oidx, odsq = oracle.binned_select_knn(K, pts.numpy(), np.array([0, n]))
+    parity.assert_knn_parity(results[2][0].cpu().numpy(), results[2][1].cpu().numpy(), oidx, odsq, what="third search")
+
+
 @pytest.mark.parametrize("maker,scale", [
     (synthetic.c1_two_events, 1.0),
     (synthetic.c2_gaussian_mixture, 0.15),

@@ -14,6 +14,7 @@ import pytest
 import torch
 
 import parity
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -64,6 +65,13 @@ def test_static_scratch_entry_point_matches_regular_one_twice():
             assert int(status.item()) == 0 and rstatus == 0
             parity.assert_knn_parity(idx.cpu().numpy(), dsq.cpu().numpy(), ridx.cpu().numpy(),
                                      rdsq.cpu().numpy(), pad_self=tf, what="static vs regular")
+            # and against the CPU oracle (the regular entry point is CUDA code as well)
+            oidx, odsq = oracle.binned_select_knn(
+                K, coords.cpu().numpy(), rs.cpu().numpy(),
+                direction=None if direction is None else direction.cpu().numpy(),
+                torch_compatible_indices=tf)
+            parity.assert_knn_parity(idx.cpu().numpy(), dsq.cpu().numpy(), oidx, odsq, pad_self=tf,
+                                     what="static vs oracle")
 
 
 def test_static_scratch_entry_point_limits_and_status():
@@ -86,6 +94,9 @@ def test_static_scratch_entry_point_limits_and_status():
         rc, idx, dsq, status = _static(cabi, bad, rs, 8, None, False)
         torch.cuda.synchronize()
         assert rc == 0 and int(status.item()) & cabi.STATUS_NONFINITE
+        # nothing was searched: every row holds the defaults of a point without neighbours
+        assert torch.equal(idx[:, 0], torch.arange(1000, device=DEV)) and bool((idx[:, 1:] == -1).all())
+        assert float(dsq.abs().max()) == 0.0
         # and a clean call afterwards works again
         good = torch.rand((1000, 3), device=DEV)
         rc, idx, dsq, status = _static(cabi, good, rs, 8, None, False)
