@@ -575,6 +575,25 @@ def run_b200(args):
     # straight into the final tensors, ids as int32 on the wire, events searched in three groups
     # so that finished rows travel while the next group is searched.  With more than one rank
     # the gathered result is compared with a single-GPU search of the whole batch on every rank.
+    def same_neighbour_rows(idx_a, dsq_a, idx_b, dsq_b):
+        """Two searches of the same points on different grids: the sorted squared distances of
+        every row must be bit-identical; the neighbour ids too, except that a row may hold a
+        different one of several candidates that tie exactly at its largest distance."""
+        if not torch.equal(torch.sort(dsq_a, 1).values, torch.sort(dsq_b, 1).values):
+            return False
+        differ = (torch.sort(idx_a, 1).values != torch.sort(idx_b, 1).values).any(1).nonzero().flatten()
+        if differ.numel() > max(1000, idx_a.shape[0] // 1000):
+            return False
+        for r in differ.tolist():
+            ia, ib = idx_a[r].tolist(), idx_b[r].tolist()
+            da, db = dsq_a[r].tolist(), dsq_b[r].tolist()
+            kth = max(da)
+            only_a = [d for i, d in zip(ia, da) if i not in set(ib)]
+            only_b = [d for i, d in zip(ib, db) if i not in set(ia)]
+            if len(only_a) != len(only_b) or any(d != kth for d in only_a + only_b):
+                return False
+        return True
+
     c3 = None
     if "c3" in sections:
         c3_local = None
@@ -616,8 +635,7 @@ def run_b200(args):
                 # neighbour sets as one GPU searching the whole batch
                 g_idx, g_dsq = c3_run("all", 3)
                 r_idx, r_dsq = fgc.binned_select_knn(w3.K, c3_coords, c3_rs)
-                c3_local["equal"] = bool(torch.equal(torch.sort(g_dsq, 1).values, torch.sort(r_dsq, 1).values)) and \
-                    bool(torch.equal(torch.sort(g_idx, 1).values, torch.sort(r_idx, 1).values))
+                c3_local["equal"] = same_neighbour_rows(g_idx, g_dsq, r_idx, r_dsq)
                 del g_idx, g_dsq, r_idx, r_dsq
         except Exception as exc:          # noqa: BLE001
             c3_local = None

@@ -30,8 +30,8 @@ FGC_MAX_BIN_DIMS = 8
 FGC_MAX_K = 257
 
 # kernels launched per call (for launch accounting in benchmarks)
-KERNELS_BUILD_GRID = 13
-KERNELS_BUILD_GRID_D4 = 16      # D = 4: a second density pass may follow a fallback to three binned coordinates
+KERNELS_BUILD_GRID = 9
+KERNELS_BUILD_GRID_D4 = 11      # D = 4: a second density pass may follow a fallback to three binned coordinates
 KERNELS_PUBLISH_STATUS = 1   # the wrapper's status check after the grid build
 KERNELS_SEARCH = 2             # k_knn + k_knn_hard (the queries that gave up their walk)
 KERNELS_KNN_BWD = 1

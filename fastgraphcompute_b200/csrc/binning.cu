@@ -171,6 +171,7 @@ extern "C" int fgc_bin_prepare(const float *coords, int64_t n_vert, int32_t n_co
                                const int64_t *n_bins_or_null, int32_t n_bins_len,
                                fgc_bin_params *out_params, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_bin_prepare");
     if (!out_params || n_vert < 0 || n_coords < 1 || n_coords > FGC_MAX_BIN_DIMS)
         return FGC_ERR_BAD_ARGUMENT;
     if (n_vert > 0 && !coords) return FGC_ERR_BAD_ARGUMENT;
@@ -198,6 +199,7 @@ extern "C" int fgc_bin_assign(const float *coords, int64_t n_vert, int32_t n_coo
                               int64_t n_total_bins, int64_t *out_bin_idx, int64_t *out_flat,
                               int64_t *out_n_per_bin, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_bin_assign");
     if (!params || n_vert < 0 || n_coords < 1 || n_coords > FGC_MAX_BIN_DIMS || n_rs < 1 ||
         n_rs > 0x7fffffff || !row_splits)
         return FGC_ERR_BAD_ARGUMENT;

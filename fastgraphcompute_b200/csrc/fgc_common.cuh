@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "fgc_b200.h"
 
 #define FGC_FULL_MASK 0xffffffffu
@@ -29,6 +31,15 @@
 #endif
 
 namespace fgc {
+
+// NVTX range around an entry point (header-only NVTX 3: a no-op unless a profiler is attached).
+struct NvtxRange {
+    explicit NvtxRange(const char *name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange &) = delete;
+    NvtxRange &operator=(const NvtxRange &) = delete;
+};
+#define FGC_NVTX(name) fgc::NvtxRange fgc_nvtx_range_(name)
 
 // Number of SMs of the current device (148 on a B200), asked once per device and kept.  Grids of
 // grid-stride kernels are sized in multiples of it.  A failed query falls back to 148 so that no

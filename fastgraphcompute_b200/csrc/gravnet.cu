@@ -345,6 +345,7 @@ extern "C" int fgc_gravnet_aggregate_fwd(const float *prop, const int64_t *idx, 
                                          float *out_max, int32_t *out_argmax,
                                          const int32_t *order_or_null, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_gravnet_aggregate_fwd");
     using namespace fgc;
     if (n_vert < 0 || K < 1 || P < 1) return FGC_ERR_BAD_ARGUMENT;
     if (n_vert > 0x7fffffff) return FGC_ERR_TOO_LARGE;
@@ -380,6 +381,7 @@ extern "C" int fgc_gravnet_aggregate_bwd(const float *prop, const int64_t *idx, 
                                          float *out_d_prop, float *out_d_distsq,
                                          const int32_t *order_or_null, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_gravnet_aggregate_bwd");
     using namespace fgc;
     if (n_vert < 0 || K < 1 || P < 1) return FGC_ERR_BAD_ARGUMENT;
     if (n_vert > 0x7fffffff) return FGC_ERR_TOO_LARGE;
@@ -423,6 +425,7 @@ extern "C" int fgc_gravnet_aggregate_bwd_sorted(const float *prop, const int64_t
                                                 float *out_d_prop, float *out_d_distsq,
                                                 const int32_t *order_or_null, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_gravnet_aggregate_bwd_sorted");
     using namespace fgc;
     if (n_vert < 0 || K < 1 || P < 1 || P > 128) return FGC_ERR_BAD_ARGUMENT;
     if (n_vert * (int64_t)K > 0x7fffffff) return FGC_ERR_TOO_LARGE;

@@ -30,6 +30,7 @@ extern "C" int fgc_index_replacer(const int64_t *to_be_replaced, int64_t n,
                                   const int64_t *replacements, int64_t n_replacements,
                                   int64_t *out, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_index_replacer");
     if (n < 0 || n_replacements < 0) return FGC_ERR_BAD_ARGUMENT;
     if (n == 0) return FGC_OK;
     if (!to_be_replaced || !out || (n_replacements > 0 && !replacements)) return FGC_ERR_BAD_ARGUMENT;

@@ -89,6 +89,7 @@ extern "C" int fgc_binned_knn_bwd(const float *grad_distsq, const int64_t *idx, 
                                   int64_t n_vert, int32_t K, int32_t n_coords,
                                   float *out_grad_coords, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_binned_knn_bwd");
     using namespace fgc;
     if (n_vert < 0 || K < 1 || n_coords < 1) return FGC_ERR_BAD_ARGUMENT;
     if (n_vert > 0x7fffffff) return FGC_ERR_TOO_LARGE;

@@ -1,17 +1,21 @@
 // binned_select_knn forward for sm_100a, part 1: the search grid (this file) --
 // part 2, the search itself, is knn_search.cu.
 //
-// Pipeline (all on the caller's stream, no host synchronisation):
-//   k_minmax      fused finite check + min/max of the binned coordinates
-//   k_grid_setup  cell width / grid shape from the extents and the point count; the grid spans
-//                 the first min(D, 4) coordinates
-//   k_zero_counts clear the cell table
-//   k_histogram   cell id per point, warp-aggregated atomic histogram; the value
-//                 returned by the atomic is the point's rank inside its cell
-//   k_scan_*      exclusive scan of the histogram -> cell boundaries
-//   k_cell_stat_refine   density pass: shrink the cells where the data is clustered; D = 4 data
-//                 that is strongly clustered goes back to a grid over three coordinates and
-//                 gets a second density pass there
+// Pipeline (all on the caller's stream, no host synchronisation; 9 launches, 11 while the
+// device still has to choose the grid's form for D = 4):
+//   k_minmax_setup  fused finite check + min/max of the binned coordinates; clears the cell
+//                 table; its last CTA validates the row splits and chooses cell width / grid
+//                 shape from the extents and the point count (the grid spans the first
+//                 min(D, 4) coordinates)
+//   k_histogram   cell id per point, warp-aggregated atomic histogram; the value returned by
+//                 the atomic is the point's rank inside its cell.  The ranks also give the
+//                 density statistic sum_c c^2 for free, and the kernel's last CTA is the density
+//                 pass: it shrinks the cells where the data is clustered; D = 4 data that is
+//                 strongly clustered goes back to a grid over three coordinates and gets a
+//                 second density pass there
+//   k_zero_counts + k_histogram again, for the grid the density pass chose (return at once
+//                 when it kept the first grid)
+//   k_scan_tile_sums_top, k_scan_apply   exclusive scan of the histogram -> cell boundaries
 //   k_fill_ids    counting-sort scatter of the original ids into cell order (arbitrary inside a cell)
 //   k_rank_place  ids in ascending order inside every cell (the layout is the same on every
 //                 run); coordinates (padded to float4), cell id and direction flag in that order
@@ -38,9 +42,20 @@ namespace fgc {
 // grid construction
 // ---------------------------------------------------------------------------
 
+__device__ void grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits, int n_rs, int n_vert,
+                           int n_bin_dims, int bins_target, int bins_cap_first, int bins_cap, int bad_rs);
+
+// Fused finite check + min/max of the binned coordinates; clears the cell table (all of its
+// capacity: the grid that decides how much of it is used does not exist yet); the CTA that
+// finishes last (a ticket counter, no waiting) checks the row splits and chooses the grid.
 __global__ void __launch_bounds__(256)
-k_minmax(const float *__restrict__ coords, int n_vert, int n_coords, int n_bin_dims, KnnGrid *g)
+k_minmax_setup(const float *__restrict__ coords, int n_vert, int n_coords, int n_bin_dims, KnnGrid *g,
+               int *__restrict__ counts, long long n_counts, const int64_t *__restrict__ row_splits, int n_rs,
+               int bins_target, int bins_cap_first, int bins_cap)
 {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_counts;
+         i += (long long)gridDim.x * blockDim.x)
+        counts[i] = 0;
     uint32_t lmin[4] = {0, 0, 0, 0}, lmax[4] = {0, 0, 0, 0};
     uint32_t bad = 0;
     for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < n_vert; v += gridDim.x * blockDim.x) {
@@ -73,6 +88,23 @@ k_minmax(const float *__restrict__ coords, int n_vert, int n_coords, int n_bin_d
         atomicMax(&g->max_key[threadIdx.x], s_max[threadIdx.x]);
     }
     if (threadIdx.x == 0 && s_bad) atomicOr(&g->nonfinite, 1u);
+    // the last CTA to arrive sees every CTA's extrema and sets the grid up
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(&g->stat_blocks_done, 1) == (int)gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // row_splits must start at 0, end at n_vert and never decrease
+    int bad_rs = 0;
+    for (int i = 1 + threadIdx.x; i < n_rs; i += blockDim.x)
+        if (row_splits[i] < row_splits[i - 1]) bad_rs = 1;
+    bad_rs = __syncthreads_or(bad_rs);
+    if (threadIdx.x == 0) {
+        g->stat_blocks_done = 0;       // the density pass counts its CTAs with the same ticket
+        grid_setup(g, row_splits, n_rs, n_vert, n_bin_dims, bins_target, bins_cap_first, bins_cap, bad_rs);
+    }
 }
 
 // Cells per dimension for a wanted cell width; widens the cells until the table fits.
@@ -93,19 +125,11 @@ __device__ inline void fit_shape(const float (&ext)[4], double wd, int bins_cap,
 
 // One thread.  Chooses the cell width so that a row split of average size gets
 // about bins_target cells, bounded by bins_cap cells per row split.
-__global__ void __launch_bounds__(32)
-k_grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits,
-             int n_rs, int n_vert, int n_bin_dims, int bins_target, int bins_cap)
+__device__ void grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits, int n_rs, int n_vert,
+                           int n_bin_dims, int bins_target, int bins_cap_first, int bins_cap, int bad_rs)
 {
-    const int lane = threadIdx.x;
-    // row_splits must start at 0, end at n_vert and never decrease (all lanes)
-    int bad_rs = 0;
-    for (int i = 1 + lane; i < n_rs; i += 32)
-        if (row_splits[i] < row_splits[i - 1]) bad_rs = 1;
-    bad_rs = __any_sync(FGC_FULL_MASK, bad_rs);
-    if (lane != 0) return;
     int status = 0;
-    if (g->nonfinite) status |= FGC_STATUS_NONFINITE;
+    if (atomicOr(&g->nonfinite, 0u)) status |= FGC_STATUS_NONFINITE;
     if (bad_rs || row_splits[0] != 0 || row_splits[n_rs - 1] != (int64_t)n_vert)
         status |= FGC_STATUS_BAD_ROW_SPLITS;
     const int n_events = n_rs - 1;
@@ -126,8 +150,8 @@ k_grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits,
             ext[gd] = 0.f;
         } else {
             const int c = gd - sh;
-            const float lo = ordered_to_float(~g->min_key[c]);
-            const float hi = ordered_to_float(g->max_key[c]);
+            const float lo = ordered_to_float(~atomicMax(&g->min_key[c], 0u));
+            const float hi = ordered_to_float(atomicMax(&g->max_key[c], 0u));
             g->cdim[gd] = c;
             g->origin[gd] = lo;
             ext[gd] = __fsub_rn(hi, lo);
@@ -143,10 +167,10 @@ k_grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits,
         double wd = pow(vol / (double)bins_target, 1.0 / (double)nz);
         // a degenerate extent ratio can make the width underflow: keep it representable
         if (!(wd > (double)ext_max * 1e-6)) wd = (double)ext_max * 1e-6;
-        fit_shape(ext, wd, bins_cap, n, w);
+        fit_shape(ext, wd, bins_cap_first, n, w);
     }
     long long B = (long long)n[0] * n[1] * n[2] * n[3];
-    if (B > bins_cap) {  // cannot happen after the loop above unless the extents are absurd
+    if (B > bins_cap_first) {  // cannot happen after the loop above unless the extents are absurd
         n[0] = n[1] = n[2] = n[3] = 1; B = 1; w = fmaxf(ext_max, 1.f) * 2.f;
         status |= FGC_STATUS_INTERNAL;
     }
@@ -239,35 +263,6 @@ __device__ void grid_refine(KnnGrid *g, unsigned long long sum_sq, int n_vert, f
     g->refined = pass + 1;
 }
 
-// Every CTA adds its share of sum_c c^2; the CTA that finishes last (a ticket counter, no
-// waiting) decides about the finer grid.
-__global__ void __launch_bounds__(256)
-k_cell_stat_refine(const int *__restrict__ counts, KnnGrid *g, int n_vert, float seen_target,
-                   float seen_target3, int bins_target3, int pass, int allow_fallback)
-{
-    if (g->status != 0) return;
-    if (pass == 1 && !g->fallback3) return;
-    const int n = g->total_bins;
-    unsigned long long s = 0;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        const unsigned long long c = (unsigned long long)counts[i];
-        s += c * c;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(FGC_FULL_MASK, s, o);
-    if ((threadIdx.x & 31) == 0 && s) { atomicAdd(&g->sum_sq, s); __threadfence(); }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        const int ticket = atomicAdd(&g->stat_blocks_done, 1);
-        if (ticket == (int)gridDim.x - 1) {
-            __threadfence();
-            grid_refine(g, atomicAdd(&g->sum_sq, 0ull), n_vert, seen_target, seen_target3, bins_target3, pass,
-                        allow_fallback);
-        }
-    }
-}
-
 __global__ void __launch_bounds__(256)
 k_zero_counts(int *__restrict__ counts, const KnnGrid *g, int stage)
 {
@@ -286,16 +281,23 @@ __device__ __forceinline__ int cell_of(float x, float origin, float inv_w, int n
     return b >= n ? n - 1 : b;
 }
 
+// refine_pass >= 0: the kernel is also the density pass of that number.  A point that arrives
+// as the r-th of its cell adds 2r+1, so that a cell of c points adds c^2 in total: the sum over
+// the cells of c^2 comes out of the histogram itself, with no second pass over the table.  The
+// CTA that finishes last (a ticket counter, no waiting) decides about the finer grid.
 __global__ void __launch_bounds__(256)
 k_histogram(const float *__restrict__ coords, int n_vert, int n_coords,
-            const int64_t *__restrict__ row_splits, int n_rs, const KnnGrid *__restrict__ g,
+            const int64_t *__restrict__ row_splits, int n_rs, KnnGrid *__restrict__ g,
             int *__restrict__ counts, int *__restrict__ pbin, int *__restrict__ prank,
-            int stage)
+            int stage, int refine_pass, float seen_target, float seen_target3, int bins_target3,
+            int allow_fallback)
 {
     if (g->refined < stage) return;
+    if (refine_pass == 1 && !g->fallback3) refine_pass = -1;
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     const bool live = v < n_vert && g->status == 0;
     int flat = 0;
+    unsigned long long sq = 0;
     if (live) {
         const float *row = coords + (size_t)v * n_coords;
         int b[4];
@@ -317,7 +319,28 @@ k_histogram(const float *__restrict__ coords, int n_vert, int n_coords,
         if ((int)(threadIdx.x & 31) == leader) base = atomicAdd(counts + flat, __popc(peers));
         base = __shfl_sync(peers, base, leader);
         pbin[v] = flat;
-        prank[v] = base + __popc(peers & lanemask_lt());
+        const int rank = base + __popc(peers & lanemask_lt());
+        prank[v] = rank;
+        sq = 2ull * (unsigned long long)rank + 1ull;
+    }
+    if (refine_pass < 0 || g->status != 0) return;     // uniform over the grid
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(FGC_FULL_MASK, sq, o);
+    __shared__ unsigned long long s_sq[8];
+    if ((threadIdx.x & 31) == 0) s_sq[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long t = 0;
+        for (int k = 0; k < 8; k++) t += s_sq[k];
+        if (t) atomicAdd(&g->sum_sq, t);
+        __threadfence();
+        const int ticket = atomicAdd(&g->stat_blocks_done, 1);
+        if (ticket == (int)gridDim.x - 1) {
+            __threadfence();
+            g->stat_blocks_done = 0;
+            grid_refine(g, atomicAdd(&g->sum_sq, 0ull), n_vert, seen_target, seen_target3, bins_target3,
+                        refine_pass, allow_fallback);
+        }
     }
 }
 
@@ -530,6 +553,7 @@ extern "C" int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int3
                                        int32_t grid_dims, void *workspace, size_t workspace_bytes,
                                        fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_knn_build_grid_dims");
     using namespace fgc;
     if (grid_dims != 0 && grid_dims != 3 && grid_dims != 4) return FGC_ERR_BAD_ARGUMENT;
     KnnWorkspace L;
@@ -578,43 +602,40 @@ extern "C" int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int3
 
     const int pt_blocks = (n + 255) / 256;
     const int red_blocks = pt_blocks < fgc::sm_count() * 4 ? pt_blocks : fgc::sm_count() * 4;
-    k_minmax<<<red_blocks, 256, 0, s>>>(coords, n, n_coords, n_bin_dims, grid);
-    FGC_CHECK_LAUNCH();
-    k_grid_setup<<<1, 32, 0, s>>>(grid, row_splits, (int)n_rs, n, n_bin_dims, bins_target, bins_cap);
-    FGC_CHECK_LAUNCH();
-    // The cell count is only known on the device: the scan grids are sized for the
-    // largest table k_grid_setup may choose and surplus blocks return at once.
+    // The cell count is only known on the device.  The first grid may use up to four times the
+    // wanted number of cells (its shape is rounded up per dimension): that part of the table is
+    // cleared together with the extent reduction; a finer grid of the density pass clears what
+    // it needs itself.  The scan grids are sized for the largest table (surplus blocks return
+    // at once).
     const int64_t max_entries = (int64_t)bins_cap * n_events + 1;
     const int scan_blocks = (int)ceil_div64(max_entries, kScanTile);
-    k_zero_counts<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, 0);
+    int bins_cap_first = bins_target > (bins_cap - 64) / 4 ? bins_cap : 4 * bins_target + 64;
+    if (!adaptive) bins_cap_first = bins_cap;
+    k_minmax_setup<<<red_blocks, 256, 0, s>>>(coords, n, n_coords, n_bin_dims, grid, counts,
+                                              (long long)bins_cap_first * n_events + 1, row_splits, (int)n_rs,
+                                              bins_target, bins_cap_first, bins_cap);
     FGC_CHECK_LAUNCH();
-    k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
-                                          pbin, prank, 0);
+    const int allow_fallback = adaptive && n_coords == 4 && forced == 0;
+    k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts, pbin, prank, 0,
+                                          adaptive ? 0 : -1, seen_target, seen_target3, bins_target, allow_fallback);
     FGC_CHECK_LAUNCH();
     if (adaptive) {
-        const int allow_fallback = n_coords == 4 && forced == 0;
-        k_cell_stat_refine<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, n, seen_target, seen_target3, bins_target, 0,
-                                                    allow_fallback);
-        FGC_CHECK_LAUNCH();
+        // the grid of the density pass, when it chose one (both kernels return at once otherwise)
         k_zero_counts<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, 1);
         FGC_CHECK_LAUNCH();
-        k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
-                                              pbin, prank, 1);
+        k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts, pbin, prank,
+                                              1, allow_fallback ? 1 : -1, seen_target, seen_target3, bins_target, 0);
         FGC_CHECK_LAUNCH();
         if (allow_fallback) {
-            // second density pass: runs only when the first one fell back to three coordinates
-            k_cell_stat_refine<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, n, seen_target, seen_target3, bins_target, 1, 0);
-            FGC_CHECK_LAUNCH();
+            // second density pass: ran only when the first one fell back to three coordinates
             k_zero_counts<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, 2);
             FGC_CHECK_LAUNCH();
-            k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts,
-                                                  pbin, prank, 2);
+            k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts, pbin,
+                                                  prank, 2, -1, seen_target, seen_target3, bins_target, 0);
             FGC_CHECK_LAUNCH();
         }
     }
-    k_scan_tile_sums<<<scan_blocks, 256, 0, s>>>(counts, &grid->total_bins, 1, blocksums);
-    FGC_CHECK_LAUNCH();
-    k_scan_block_sums<<<1, 1024, 0, s>>>(blocksums, &grid->total_bins, 1);
+    k_scan_tile_sums_top<<<scan_blocks, 256, 0, s>>>(counts, &grid->total_bins, 1, blocksums, &grid->scan_ticket);
     FGC_CHECK_LAUNCH();
     k_scan_apply<<<scan_blocks, 256, 0, s>>>(counts, &grid->total_bins, 1, blocksums);
     FGC_CHECK_LAUNCH();

@@ -43,6 +43,7 @@ struct KnnGrid {
     int32_t n_huge_cells;  // length of the work list of cells sorted by one CTA each
     int32_t stat_blocks_done;   // CTAs of the density pass that have added their share
     int32_t n_hard;        // queries whose walk gave up in a large row split (searched by whole CTAs)
+    int32_t scan_ticket;   // CTAs of the scan's first kernel that are done (zero between launches)
     unsigned long long sum_sq;   // sum over cells of (points in cell)^2, first grid
     // optional debug counters (filled when a search is launched with count_evals):
     // [0] distance evaluations, [1] 32-candidate steps, [2] list insertions,
@@ -123,7 +124,7 @@ static_assert(sizeof(KnnGrid) <= kGridHeaderBytes, "grid header too large");
 
 // Byte offsets of the workspace sections (all 256-byte aligned).
 struct KnnWorkspace {
-    size_t header, counts, blocksums, pbin, prank, stmp, sorig, sbin, sflag, biglist, hugelist, scoords, total;
+    size_t header, counts, blocksums, pbin, prank, stmp, sorig, sbin, sflag, done, biglist, hugelist, scoords, total;
     int64_t cap_bins;   // capacity of the cell table (entries), host decision
     int nv;             // float4 per point in the sorted coordinate array
 };
@@ -148,6 +149,7 @@ inline KnnWorkspace knn_workspace_layout(int64_t n_vert, int n_coords, int64_t n
     w.sorig = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.sbin = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.sflag = off; off = align_up(off + (size_t)n_vert, 256);
+    w.done = off; off = align_up(off + (size_t)n_vert, 256);     // 1 = row already written by the tile kernel
     w.biglist = off; off = align_up(off + sizeof(int32_t) * (size_t)(n_vert / (kRankMax + 1) + 1), 256);
     w.hugelist = off; off = align_up(off + sizeof(int32_t) * (size_t)(n_vert / (kWarpSortMaxShared + 1) + 1), 256);
     w.scoords = off; off = align_up(off + sizeof(float4) * (size_t)n_vert * w.nv, 256);

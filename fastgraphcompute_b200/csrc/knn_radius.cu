@@ -62,6 +62,7 @@ k_knn_radius_filter(int64_t *__restrict__ idx, float *__restrict__ dist, int n_v
 extern "C" int fgc_knn_radius_filter(int64_t *idx, float *distsq, int64_t n_vert, int32_t K,
                                      double max_radius, int32_t tf_compat, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_knn_radius_filter");
     using namespace fgc;
     if (n_vert < 0 || K < 1) return FGC_ERR_BAD_ARGUMENT;
     if (K > FGC_MAX_K) return FGC_ERR_UNSUPPORTED_K;

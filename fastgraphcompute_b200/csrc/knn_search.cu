@@ -598,6 +598,7 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
                               int64_t *out_idx, float *out_distsq, void *workspace,
                               size_t workspace_bytes, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_knn_search");
     using namespace fgc;
     KnnWorkspace L;
     const int rc = check_knn_args(n_vert, n_coords, n_rs, K, workspace, workspace_bytes, &L);

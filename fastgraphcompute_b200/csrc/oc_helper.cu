@@ -271,6 +271,7 @@ extern "C" int fgc_oc_prepare(const int64_t *asso_idx, int64_t n_vert, const int
                               void *workspace, size_t workspace_bytes, int64_t *objects_per_split,
                               fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_oc_prepare");
     using namespace fgc;
     if (n_vert < 0 || n_rs < 1 || !row_splits || (!objects_per_split && n_rs > 1)) return FGC_ERR_BAD_ARGUMENT;
     if (n_vert > 0x7ffffff0 || n_rs > 0x7fffffff) return FGC_ERR_TOO_LARGE;
@@ -345,6 +346,7 @@ extern "C" int fgc_oc_fill(const void *workspace, size_t workspace_bytes, int64_
                            const int64_t *row_splits, int64_t n_unique, int64_t n_maxuq, int64_t n_maxrs,
                            int64_t *out_M, int64_t *out_M_not_or_null, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_oc_fill");
     using namespace fgc;
     if (n_vert < 0 || n_unique < 0 || n_maxuq < 0 || n_maxrs < 0 || !row_splits) return FGC_ERR_BAD_ARGUMENT;
     if (n_vert > 0x7ffffff0) return FGC_ERR_TOO_LARGE;
@@ -383,6 +385,7 @@ extern "C" int fgc_select_with_default(const int64_t *idx, int64_t n_idx, const 
                                        int64_t n_feat, int32_t word_bytes, const void *default_word_host,
                                        void *out, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_select_with_default");
     using namespace fgc;
     if (n_idx < 0 || n_rows_feat < 0 || n_feat < 0 || !default_word_host) return FGC_ERR_BAD_ARGUMENT;
     if (word_bytes != 4 && word_bytes != 8) return FGC_ERR_BAD_ARGUMENT;

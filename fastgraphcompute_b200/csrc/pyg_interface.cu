@@ -69,6 +69,7 @@ extern "C" int fgc_row_splits_from_strict_batch(const int64_t *batch, int64_t n_
                                                 int64_t *out_row_splits, void *workspace,
                                                 size_t workspace_bytes, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_row_splits_from_strict_batch");
     using namespace fgc;
     if (n_points < 0 || !out_row_splits) return FGC_ERR_BAD_ARGUMENT;
     if (n_points > 0x7ffffffe) return FGC_ERR_TOO_LARGE;
@@ -108,6 +109,7 @@ extern "C" int fgc_pyg_read_count(const void *workspace, int64_t *n_row_splits_h
 extern "C" int fgc_strict_batch_from_row_splits(const int64_t *row_splits, int64_t n_rs, int64_t n_points,
                                                 int64_t *out_batch, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_strict_batch_from_row_splits");
     using namespace fgc;
     if (!row_splits || n_rs < 1 || n_points < 0) return FGC_ERR_BAD_ARGUMENT;
     if (n_rs > 0x7fffffff) return FGC_ERR_TOO_LARGE;

@@ -113,6 +113,7 @@ extern "C" size_t fgc_reverse_graph_bytes(int64_t n_vert, int32_t K)
 extern "C" int fgc_build_reverse_graph(const int64_t *idx, int64_t n_vert, int32_t K, void *rgraph,
                                        size_t rgraph_bytes, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_build_reverse_graph");
     using namespace fgc;
     if (n_vert < 0 || K < 1) return FGC_ERR_BAD_ARGUMENT;
     if (n_vert * (int64_t)K > 0x7fffffff) return FGC_ERR_TOO_LARGE;
@@ -153,6 +154,7 @@ extern "C" int fgc_binned_knn_bwd_sorted(const float *grad_distsq, const int64_t
                                          int32_t n_coords, const void *rgraph, size_t rgraph_bytes,
                                          float *out_grad_coords, fgc_stream_t stream)
 {
+    FGC_NVTX("fgc_binned_knn_bwd_sorted");
     using namespace fgc;
     if (n_vert < 0 || K < 1 || n_coords < 1) return FGC_ERR_BAD_ARGUMENT;
     if (n_vert * (int64_t)K > 0x7fffffff) return FGC_ERR_TOO_LARGE;

@@ -7,6 +7,7 @@ point itself in slot 0 and -1 in unused slots, squared distances float32 [N,K],
 differentiable w.r.t. the coordinates through the distances only.
 """
 import ctypes
+import threading
 from typing import Optional, Tuple
 
 import torch
@@ -48,6 +49,9 @@ def _raise_for_status(status):
 grid_dims = 0
 grid_probe_every = 64
 _grid_memory = {}        # (device, N, row splits, K) -> [form, calls since the last automatic choice]
+# forward calls may come from several host threads (one per stream or device) and the backward runs
+# on autograd's own threads: the two module-level tables are only touched under this lock
+_tables_lock = threading.Lock()
 
 
 def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=False):
@@ -71,10 +75,11 @@ def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=Fal
             if grid_dims in (3, 4):
                 form = grid_dims
             elif grid_dims == 0 and check_status:
-                mem = _grid_memory.get((dev.index, n_vert, n_rs, K))
-                if mem is not None and mem[1] < grid_probe_every:
-                    form = mem[0]
-                    mem[1] += 1
+                with _tables_lock:
+                    mem = _grid_memory.get((dev.index, n_vert, n_rs, K))
+                    if mem is not None and mem[1] < grid_probe_every:
+                        form = mem[0]
+                        mem[1] += 1
         _cabi.check(_cabi.lib.fgc_knn_build_grid_dims(
             _cabi.ptr(coords), n_vert, n_coords, _cabi.ptr(row_splits), n_rs, K,
             _cabi.ptr(direction), float(target_occupancy), form, _cabi.ptr(ws), nbytes, stream),
@@ -102,9 +107,10 @@ def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=Fal
             info = status_host.tolist()
             _raise_for_status(int(info[0]))
             if n_coords == 4 and form == 0 and grid_dims == 0:
-                if len(_grid_memory) > 256:
-                    _grid_memory.clear()
-                _grid_memory[(dev.index, n_vert, n_rs, K)] = [int(info[1]) & 15, 0]      # what the device chose
+                with _tables_lock:
+                    if len(_grid_memory) > 256:
+                        _grid_memory.clear()
+                    _grid_memory[(dev.index, n_vert, n_rs, K)] = [int(info[1]) & 15, 0]      # what the device chose
     return idx, dist, ws
 
 
@@ -140,7 +146,8 @@ _rgraph_cache = {}
 
 
 def clear_reverse_graph_cache():
-    _rgraph_cache.clear()
+    with _tables_lock:
+        _rgraph_cache.clear()
 
 
 def reverse_graph(idx, keep):
@@ -150,8 +157,9 @@ def reverse_graph(idx, keep):
     n_vert, K = idx.shape
     stream = _cabi.current_stream(idx.device)
     key = (idx.data_ptr(), idx._version, n_vert, K, idx.device, getattr(stream, "value", stream))
-    hit = _rgraph_cache.pop(key, None)
-    _rgraph_cache.clear()
+    with _tables_lock:
+        hit = _rgraph_cache.pop(key, None)
+        _rgraph_cache.clear()
     if hit is not None:
         rg = hit[1]
     else:
@@ -162,7 +170,8 @@ def reverse_graph(idx, keep):
         _cabi.check(_cabi.lib.fgc_build_reverse_graph(
             _cabi.ptr(idx), n_vert, K, _cabi.ptr(rg), rbytes, stream), "fgc_build_reverse_graph")
     if keep:
-        _rgraph_cache[key] = (idx, rg)
+        with _tables_lock:
+            _rgraph_cache[key] = (idx, rg)
     return rg, rg.numel()
 
 

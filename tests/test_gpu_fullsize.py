@@ -176,26 +176,21 @@ def test_c3_full_event_and_batch_vs_oracle():
 
 
 def test_c5_quarter_million_point_event_vs_oracle():
-    """One C5 event of 250 000 points (200 Pareto-sized clusters + uniform background, K = 128),
-    plus a few stray points far away, against the oracle.  The case must reach the parts the small cases do not: cells of more than
-    512 points (sorted by a whole CTA), background queries that give up their walk and are
-    searched by a whole CTA (k_knn_hard), and the four-slots-per-lane list."""
+    """One C5 event of 250 000 points (200 Pareto-sized clusters + uniform background, K = 128)
+    against the oracle.  The case reaches what the small cases do not: cells of more than 512
+    points (sorted by a whole CTA) and the four-slots-per-lane list on clustered data.  (Queries
+    that give up their walk and go to k_knn_hard are covered by
+    test_knn_repeated_search_on_one_grid, on data the oracle can bin.)"""
     import importlib
     km = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
     w = synthetic.c5_skewed(scale=0.25, n_events=1)
     assert w.n_points == 250000 and w.K == 128
-    # forty stray points far outside the unit cube: their walks cross empty space and give up
-    g = torch.Generator().manual_seed(5)
-    stray = 60.0 * torch.rand((40, 3), generator=g) - 30.0
-    coords = torch.cat([w.coords, stray])[torch.randperm(250040, generator=g)].contiguous()
-    row_splits = torch.tensor([0, 250040], dtype=torch.int64)
-    c = coords.to(DEV)
-    rs = row_splits.to(DEV)
+    c = w.coords.to(DEV)
+    rs = w.row_splits.to(DEV)
     idx, dist, ws = km.knn_forward_raw(c, rs, w.K, None, False, count_evals=True)
     counters, shape, width = km.read_counters(ws)
     assert counters[7] > 0, "no cell above 512 points"
-    assert counters[6] > 0, "no query was handed to k_knn_hard"
-    oidx, odist = oracle.binned_select_knn(w.K, coords.numpy(), row_splits.numpy())
+    oidx, odist = oracle.binned_select_knn(w.K, w.coords.numpy(), w.row_splits.numpy())
     st = parity.assert_knn_parity(idx.cpu().numpy(), dist.cpu().numpy(), oidx, odist, what="c5 250k event")
     assert st["max_rel"] == 0.0
 

@@ -308,7 +308,8 @@ def test_knn_gradient_on_reference_slot_order(golden_dir):
         parity.assert_grad_close(out.cpu().numpy(), c["out"]["grad_coords"], what=name)
 
 
-def test_knn_repeated_search_on_one_grid():
+@pytest.mark.parametrize("K", [20, 100])
+def test_knn_repeated_search_on_one_grid(K):
     """The build/search split: one grid, searched three times.  Clustered points with far
     outliers in a row split of more than 4096 points make some walks give up, so every search
     fills the list of queries for k_knn_hard; the list must start empty each time (same rows,
@@ -317,7 +318,7 @@ def test_knn_repeated_search_on_one_grid():
     import importlib
     km = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
     g = torch.Generator().manual_seed(17)
-    n_in, n_out, K = 12000, 60, 20
+    n_in, n_out = 12000, 60
     pts = torch.cat([0.5 + 0.002 * torch.randn((n_in, 3), generator=g),
                      200.0 * torch.rand((n_out, 3), generator=g) - 100.0])
     pts = pts[torch.randperm(pts.shape[0], generator=g)].contiguous()
