@@ -98,6 +98,8 @@ SIGNATURES = {
     "fgc_publish_status": (ctypes.c_int, [c_void_p, c_void_p, c_void_p]),
     "fgc_binned_knn_bwd": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i32, c_i32,
                                           c_void_p, c_void_p]),
+    "fgc_binned_knn_bwd_ordered": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i32, c_i32, c_void_p,
+                                                  c_void_p, c_void_p]),
     "fgc_reverse_graph_bytes": (c_size, [c_i64, c_i32]),
     "fgc_build_reverse_graph": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_void_p, c_size, c_void_p]),
     "fgc_binned_knn_bwd_sorted": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i32, c_i32,

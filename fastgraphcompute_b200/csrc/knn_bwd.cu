@@ -10,6 +10,12 @@
 // coordinate, the neighbour term leaves as one reduction per slot: a 16-byte
 // (D = 4) or 8-byte (D = 2) vector reduction, else one fp32 reduction per
 // coordinate.
+//
+// `order` (optional) is a permutation of the rows: warp w works on row order[w].  Given the
+// cell order of the search that produced idx, the warps of a CTA work on rows of one cell or of
+// neighbouring cells, whose neighbour sets largely coincide: the scattered 16-byte gathers of
+// neighbour coordinates hit in L1, and the reductions of one CTA go to few L2 lines.  The
+// gradient does not depend on it (up to the order of the float additions).
 #include "fgc_common.cuh"
 
 namespace fgc {
@@ -20,11 +26,13 @@ template <int D>
 __global__ void __launch_bounds__(kBwdWarps * 32)
 k_knn_bwd(const float *__restrict__ grad_distsq, const int64_t *__restrict__ idx,
           const float *__restrict__ coords, int n_vert, int K, int n_coords_rt,
-          float *__restrict__ out, int vec_ok)
+          float *__restrict__ out, int vec_ok, const int32_t *__restrict__ order)
 {
     const int lane = threadIdx.x & 31;
-    const int i = blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
-    if (i >= n_vert) return;
+    const int wi = blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
+    if (wi >= n_vert) return;
+    const int i = order ? __ldg(order + wi) : wi;
+    if (i < 0 || i >= n_vert) return;
     const int nc = D > 0 ? D : n_coords_rt;
     constexpr int DM = D > 0 ? D : 1;
     if (D > 0) {
@@ -89,6 +97,15 @@ extern "C" int fgc_binned_knn_bwd(const float *grad_distsq, const int64_t *idx, 
                                   int64_t n_vert, int32_t K, int32_t n_coords,
                                   float *out_grad_coords, fgc_stream_t stream)
 {
+    return fgc_binned_knn_bwd_ordered(grad_distsq, idx, coords, n_vert, K, n_coords, nullptr, out_grad_coords,
+                                      stream);
+}
+
+extern "C" int fgc_binned_knn_bwd_ordered(const float *grad_distsq, const int64_t *idx, const float *coords,
+                                          int64_t n_vert, int32_t K, int32_t n_coords,
+                                          const int32_t *order_or_null, float *out_grad_coords,
+                                          fgc_stream_t stream)
+{
     FGC_NVTX("fgc_binned_knn_bwd");
     using namespace fgc;
     if (n_vert < 0 || K < 1 || n_coords < 1) return FGC_ERR_BAD_ARGUMENT;
@@ -102,10 +119,10 @@ extern "C" int fgc_binned_knn_bwd(const float *grad_distsq, const int64_t *idx, 
     const int T = kBwdWarps * 32;
     const int vec_ok = ((uintptr_t)out_grad_coords & 15) == 0;
     switch (n_coords) {
-    case 2: k_knn_bwd<2><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok); break;
-    case 3: k_knn_bwd<3><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok); break;
-    case 4: k_knn_bwd<4><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok); break;
-    default: k_knn_bwd<0><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok); break;
+    case 2: k_knn_bwd<2><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
+    case 3: k_knn_bwd<3><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
+    case 4: k_knn_bwd<4><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
+    default: k_knn_bwd<0><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
     }
     FGC_CHECK_LAUNCH();
     return FGC_OK;

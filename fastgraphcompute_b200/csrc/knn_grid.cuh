@@ -124,7 +124,7 @@ static_assert(sizeof(KnnGrid) <= kGridHeaderBytes, "grid header too large");
 
 // Byte offsets of the workspace sections (all 256-byte aligned).
 struct KnnWorkspace {
-    size_t header, counts, blocksums, pbin, prank, stmp, sorig, sbin, sflag, done, biglist, hugelist, scoords, total;
+    size_t header, counts, blocksums, pbin, prank, stmp, sorig, sbin, sflag, biglist, hugelist, scoords, total;
     int64_t cap_bins;   // capacity of the cell table (entries), host decision
     int nv;             // float4 per point in the sorted coordinate array
 };
@@ -149,7 +149,6 @@ inline KnnWorkspace knn_workspace_layout(int64_t n_vert, int n_coords, int64_t n
     w.sorig = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.sbin = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);
     w.sflag = off; off = align_up(off + (size_t)n_vert, 256);
-    w.done = off; off = align_up(off + (size_t)n_vert, 256);     // 1 = row already written by the tile kernel
     w.biglist = off; off = align_up(off + sizeof(int32_t) * (size_t)(n_vert / (kRankMax + 1) + 1), 256);
     w.hugelist = off; off = align_up(off + sizeof(int32_t) * (size_t)(n_vert / (kWarpSortMaxShared + 1) + 1), 256);
     w.scoords = off; off = align_up(off + sizeof(float4) * (size_t)n_vert * w.nv, 256);

@@ -175,8 +175,9 @@ def reverse_graph(idx, keep):
     return rg, rg.numel()
 
 
-def knn_backward_raw(grad_dist, idx, coords):
-    """Launch the backward (atomic or sorted-segment variant) on prepared tensors."""
+def knn_backward_raw(grad_dist, idx, coords, order=None):
+    """Launch the backward (atomic or sorted-segment variant) on prepared tensors.  order: the
+    forward's cell order (int32 [N]) as processing order of the atomic variant, or None."""
     n_vert, n_coords = coords.shape
     K = idx.shape[1]
     out = torch.empty_like(coords)
@@ -188,9 +189,9 @@ def knn_backward_raw(grad_dist, idx, coords):
                 _cabi.ptr(grad_dist), _cabi.ptr(idx), _cabi.ptr(coords), n_vert, K, n_coords,
                 _cabi.ptr(rg), rbytes, _cabi.ptr(out), stream), "fgc_binned_knn_bwd_sorted")
         else:
-            _cabi.check(_cabi.lib.fgc_binned_knn_bwd(
+            _cabi.check(_cabi.lib.fgc_binned_knn_bwd_ordered(
                 _cabi.ptr(grad_dist), _cabi.ptr(idx), _cabi.ptr(coords), n_vert, K,
-                n_coords, _cabi.ptr(out), stream), "fgc_binned_knn_bwd")
+                n_coords, _cabi.ptr(order), _cabi.ptr(out), stream), "fgc_binned_knn_bwd_ordered")
     return out
 
 
@@ -204,7 +205,7 @@ class _BinnedKNN(torch.autograd.Function):
         _cabi.require_cuda(coords, "coords")
         idx, dist, ws = knn_forward_raw(coords, row_splits, K, direction, tf_compat)
         order = cell_order(ws, coords.shape[0], coords.shape[1], row_splits.numel(), K).clone()
-        ctx.save_for_backward(idx, coords)
+        ctx.save_for_backward(idx, coords, order)
         ctx.mark_non_differentiable(idx, order)
         # no zero tensors for the gradients of idx and order (an int64 [N, K] fill per backward)
         ctx.set_materialize_grads(False)
@@ -212,12 +213,13 @@ class _BinnedKNN(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_idx, grad_dist, grad_order):
-        idx, coords = ctx.saved_tensors
+        idx, coords, order = ctx.saved_tensors
         if not ctx.needs_input_grad[0]:
             return None, None, None, None, None
         if grad_dist is None:
             return torch.zeros_like(coords), None, None, None, None
-        return knn_backward_raw(grad_dist.to(dtype=torch.float32).contiguous(), idx, coords), None, None, None, None
+        return (knn_backward_raw(grad_dist.to(dtype=torch.float32).contiguous(), idx, coords, order),
+                None, None, None, None)
 
 
 def binned_select_knn_with_order(K: int, coords: torch.Tensor, row_splits: torch.Tensor,

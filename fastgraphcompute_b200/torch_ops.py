@@ -9,7 +9,7 @@ calls the C ABI of libfgc_b200.so; autograd is attached with ``register_autograd
 inference with ``register_fake``.
 
     torch.ops.fgc_b200.knn_forward(coords, row_splits, K, direction, tf_compat) -> (idx, distsq, order)
-    torch.ops.fgc_b200.knn_backward(grad_distsq, idx, coords) -> grad_coords
+    torch.ops.fgc_b200.knn_backward(grad_distsq, idx, coords, order) -> grad_coords
     torch.ops.fgc_b200.gravnet_aggregate(prop, idx, distsq, order) -> (mean, max, argmax)
     torch.ops.fgc_b200.gravnet_aggregate_backward(...) -> (d_prop, d_distsq)
     torch.ops.fgc_b200.index_replacer(to_be_replaced, replacements) -> replaced
@@ -59,30 +59,32 @@ def _(coords, row_splits, K, direction, tf_compat):
 
 
 @torch.library.custom_op("fgc_b200::knn_backward", mutates_args=())
-def knn_backward(grad_distsq: Tensor, idx: Tensor, coords: Tensor) -> Tensor:
+def knn_backward(grad_distsq: Tensor, idx: Tensor, coords: Tensor, order: Optional[Tensor]) -> Tensor:
     _cabi.require_cuda(coords, "coords")
     grad_distsq = grad_distsq.to(torch.float32).contiguous()
     idx = idx.to(torch.int64).contiguous()
     coords = coords.to(torch.float32).contiguous()
-    return _knn.knn_backward_raw(grad_distsq, idx, coords)
+    if order is not None:
+        order = order.to(torch.int32).contiguous()
+    return _knn.knn_backward_raw(grad_distsq, idx, coords, order)
 
 
 @knn_backward.register_fake
-def _(grad_distsq, idx, coords):
+def _(grad_distsq, idx, coords, order):
     return torch.empty_like(coords, dtype=torch.float32)
 
 
 def _knn_setup(ctx, inputs, output):
     coords = inputs[0]
     idx = output[0]
-    ctx.save_for_backward(idx, coords)
+    ctx.save_for_backward(idx, coords, output[2])
 
 
 def _knn_grad(ctx, g_idx, g_dist, g_order):
-    idx, coords = ctx.saved_tensors
+    idx, coords, order = ctx.saved_tensors
     if g_dist is None:
         return torch.zeros_like(coords), None, None, None, None
-    return torch.ops.fgc_b200.knn_backward(g_dist, idx, coords.to(torch.float32)), None, None, None, None
+    return torch.ops.fgc_b200.knn_backward(g_dist, idx, coords.to(torch.float32), order), None, None, None, None
 
 
 knn_forward.register_autograd(_knn_grad, setup_context=_knn_setup)
@@ -250,7 +252,7 @@ def register_reference_op_names():
         return idx, dist
 
     def knn_grad(grad_distances, indices, distances, coordinates):
-        return torch.ops.fgc_b200.knn_backward(grad_distances, indices, coordinates)
+        return torch.ops.fgc_b200.knn_backward(grad_distances, indices, coordinates, None)
 
     def knn_on_binned_input(coordinates, bin_idx, dim_bin_idx, bin_boundaries, n_bins, bin_width, direction,
                             tf_compat, use_direction, K):

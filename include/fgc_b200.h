@@ -279,6 +279,17 @@ int fgc_publish_status(const void *workspace_or_params, int32_t *status_mapped, 
 int fgc_binned_knn_bwd(const float *grad_distsq, const int64_t *idx, const float *coords,
                        int64_t n_vert, int32_t K, int32_t n_coords, float *out_grad_coords,
                        fgc_stream_t stream);
+/*
+ * The same with a processing order: order_or_null [n_vert] int32, a permutation of the rows
+ * (fgc_knn_cell_order of the forward's workspace, copied before the workspace is reused).
+ * Rows that are neighbours in space are then processed by the same CTA, which makes the
+ * scattered reads and reductions local (C2: 0.10 -> 0.08 ms).  The gradient is the same up to
+ * the order of the float additions.  No counterpart in the reference.
+ */
+int fgc_binned_knn_bwd_ordered(const float *grad_distsq, const int64_t *idx, const float *coords,
+                               int64_t n_vert, int32_t K, int32_t n_coords,
+                               const int32_t *order_or_null, float *out_grad_coords,
+                               fgc_stream_t stream);
 
 /*
  * Deterministic variant of the backward: sorted-segment reductions instead of float atomics.
