@@ -1,7 +1,7 @@
 // Ascending in-place sort of a short int32 segment by one warp (keys are distinct).
 //   up to 32 keys            bitonic network in registers, one key per lane
 //   up to kWarpSortMaxShared bitonic network in shared memory (caller provides the buffer)
-//   longer                   selection sort by the warp, in place (rare)
+//   longer                   bitonic sort by the warp, in place in global memory (rare)
 #pragma once
 #include "fgc_common.cuh"
 
@@ -43,16 +43,34 @@ __device__ __forceinline__ void warp_sort_segment(int *seg, int n, int *keys, in
         for (int t = lane; t < n; t += 32) seg[t] = keys[t];
         __syncwarp();
     } else {
-        for (int p = 0; p < n - 1; p++) {
-            int best = 0x7fffffff, where = -1;
-            for (int t = p + lane; t < n; t += 32) {
-                const int v = seg[t];
-                if (v < best) { best = v; where = t; }
+        // Bitonic sort in its all-ascending form, in place in global memory, by this one warp:
+        // O(n log^2 n / 32) steps (a hub point of a reverse neighbour graph can have a segment of
+        // 10^5 entries or more; a quadratic method would keep the GPU busy for minutes).  The
+        // sequence is treated as padded to a power of two with +infinity; a compare-exchange
+        // whose upper partner lies in the padding never swaps, so it is simply skipped.
+        int P = 1;
+        while (P < n) P <<= 1;
+        for (int k = 2; k <= P; k <<= 1) {
+            // flip: element i of a block of k against its mirror image
+            for (int t = lane; t < P / 2; t += 32) {
+                const int half = k >> 1, blk = t / half, off = t - blk * half;
+                const int a = blk * k + off, b = blk * k + (k - 1 - off);
+                if (b < n) {
+                    const int ka = seg[a], kb = seg[b];
+                    if (ka > kb) { seg[a] = kb; seg[b] = ka; }
+                }
             }
-            const int gmin = __reduce_min_sync(FGC_FULL_MASK, best);
-            const unsigned who = __ballot_sync(FGC_FULL_MASK, best == gmin);
-            if (lane == __ffs(who) - 1 && where != p) { seg[where] = seg[p]; seg[p] = gmin; }
             __syncwarp();
+            for (int j = k >> 2; j > 0; j >>= 1) {
+                for (int t = lane; t < P / 2; t += 32) {
+                    const int a = 2 * j * (t / j) + (t % j), b = a + j;
+                    if (b < n) {
+                        const int ka = seg[a], kb = seg[b];
+                        if (ka > kb) { seg[a] = kb; seg[b] = ka; }
+                    }
+                }
+                __syncwarp();
+            }
         }
     }
 }

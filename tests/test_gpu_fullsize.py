@@ -80,6 +80,16 @@ def test_c2_full_vs_oracle_and_properties():
     (dist * w.grad_distsq.to(DEV)).sum().backward()
     og = oracle.binned_select_knn_grad(w.grad_distsq.numpy(), idx.cpu().numpy(), w.coords.numpy())
     parity.assert_grad_close(c.grad.cpu().numpy(), og, what="c2 full grad")
+    # The rule above is scaled by the gradient's RMS (sums of up to a few hundred terms that
+    # cancel cannot be compared element-relative where the result is near zero).  On the elements
+    # that are NOT small -- magnitude above the RMS -- the plain element-relative error is bounded
+    # as well; it is printed (pytest -s) for the record.
+    mine = c.grad.cpu().numpy().astype(np.float64)
+    ref = og.astype(np.float64)
+    big = np.abs(ref) > np.sqrt(np.mean(ref * ref))
+    rel = float(np.max(np.abs(mine[big] - ref[big]) / np.abs(ref[big])))
+    print("c2 gradient: max element-relative error on |g| > RMS: %.3g (%d elements)" % (rel, int(big.sum())))
+    assert rel <= 1e-5
 
 
 def test_c3_full_properties():

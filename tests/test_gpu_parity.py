@@ -603,8 +603,16 @@ def test_knn_backward_sorted_segments_is_bit_reproducible(golden_dir):
             assert torch.equal(grads[0], grads[1]) and torch.equal(grads[0], grads[2])
             og = oracle.binned_select_knn_grad(w.grad_distsq.numpy(), og_idx, w.coords.numpy())
             parity.assert_grad_close(grads[0].cpu().numpy(), og, what=w.name + " sorted-segment grad")
-        # a hub: every point lists point 0 (in-degree 3000 > the shared-memory sort limit)
-        n, k = 3000, 4
+        # a hub: every point lists point 0 (in-degree above the shared-memory sort limit; the
+        # second size is far beyond what a quadratic sort of the hub's segment could finish)
+        for n, k in ((3000, 4), (70001, 4)):
+            _check_hub(n, k)
+    finally:
+        km.deterministic_backward = False
+
+
+def _check_hub(n, k):
+    if True:
         g = torch.Generator().manual_seed(2)
         coords = torch.rand((n, 3), generator=g)
         idx = torch.stack([torch.arange(n), torch.zeros(n, dtype=torch.int64),
@@ -620,9 +628,7 @@ def test_knn_backward_sorted_segments_is_bit_reproducible(golden_dir):
         assert _cabi.lib.fgc_binned_knn_bwd_sorted(_cabi.ptr(cg), _cabi.ptr(ci), _cabi.ptr(cc), n, k, 3,
                                                    _cabi.ptr(rg), rb, _cabi.ptr(out), st) == 0
         og = oracle.binned_select_knn_grad(gd.numpy(), idx.numpy(), coords.numpy())
-        parity.assert_grad_close(out.cpu().numpy(), og, what="hub")
-    finally:
-        km.deterministic_backward = False
+        parity.assert_grad_close(out.cpu().numpy(), og, what="hub %d" % n)
 
 
 def test_gravnet_training_step_is_bit_reproducible_with_sorted_segment_backwards():
