@@ -308,6 +308,39 @@ def test_knn_gradient_on_reference_slot_order(golden_dir):
         parity.assert_grad_close(out.cpu().numpy(), c["out"]["grad_coords"], what=name)
 
 
+def test_knn_and_backward_stay_inside_their_output_buffers():
+    """Canary check through the C ABI: outputs carved out of larger buffers whose guard zones (before
+    and after, filled with a sentinel) must come back untouched; the workspace gets a guard behind
+    its declared size too.  Several shapes incl. an empty event, pads and K above 32."""
+    from fastgraphcompute_b200 import _cabi
+    g = torch.Generator().manual_seed(23)
+    guard = 4096
+    for n, d, K, rs_list in ((5000, 3, 17, [0, 1200, 1200, 5000]), (3001, 4, 40, [0, 9, 3001]), (777, 2, 64, [0, 777])):
+        coords = torch.rand((n, d), generator=g).to(DEV)
+        rs = torch.tensor(rs_list, dtype=torch.int64, device=DEV)
+        big_i = torch.full((n * K + 2 * guard,), -77, dtype=torch.int64, device=DEV)
+        big_d = torch.full((n * K + 2 * guard,), -77.0, dtype=torch.float32, device=DEV)
+        idx = big_i[guard: guard + n * K].view(n, K)
+        dsq = big_d[guard: guard + n * K].view(n, K)
+        nb = _cabi.lib.fgc_knn_workspace_bytes(n, d, rs.numel(), K)
+        big_ws = torch.full((nb + guard,), 0x5a, dtype=torch.uint8, device=DEV)
+        st = _cabi.current_stream(coords.device)
+        assert _cabi.lib.fgc_binned_knn_fwd(_cabi.ptr(coords), n, d, _cabi.ptr(rs), rs.numel(), K, None, 0, 0.0,
+                                            _cabi.ptr(idx), _cabi.ptr(dsq), _cabi.ptr(big_ws), nb, st) == 0
+        gd = torch.randn((n, K), generator=g).to(DEV)
+        big_g = torch.full((n * d + 2 * guard,), -77.0, dtype=torch.float32, device=DEV)
+        grad = big_g[guard: guard + n * d].view(n, d)
+        assert _cabi.lib.fgc_binned_knn_bwd(_cabi.ptr(gd), _cabi.ptr(idx), _cabi.ptr(coords), n, K, d,
+                                            _cabi.ptr(grad), st) == 0
+        torch.cuda.synchronize()
+        for big, sentinel in ((big_i, -77), (big_d, -77.0), (big_g, -77.0)):
+            assert bool((big[:guard] == sentinel).all()) and bool((big[-guard:] == sentinel).all())
+        assert bool((big_ws[nb:] == 0x5a).all())
+        assert int(idx.min()) >= -1 and int(idx.max()) < n and bool(torch.isfinite(grad).all())
+        oidx, odsq = oracle.binned_select_knn(K, coords.cpu().numpy(), rs.cpu().numpy())
+        parity.assert_knn_parity(idx.cpu().numpy(), dsq.cpu().numpy(), oidx, odsq, what="canary case")
+
+
 @pytest.mark.parametrize("K", [20, 100])
 def test_knn_repeated_search_on_one_grid(K):
     """The build/search split: one grid, searched three times.  Clustered points with far
@@ -628,7 +661,9 @@ def _check_hub(n, k):
         assert _cabi.lib.fgc_binned_knn_bwd_sorted(_cabi.ptr(cg), _cabi.ptr(ci), _cabi.ptr(cc), n, k, 3,
                                                    _cabi.ptr(rg), rb, _cabi.ptr(out), st) == 0
         og = oracle.binned_select_knn_grad(gd.numpy(), idx.numpy(), coords.numpy())
-        parity.assert_grad_close(out.cpu().numpy(), og, what="hub %d" % n)
+        # the hub's own gradient is a sum of n terms, added here in a fixed tree order and in the
+        # oracle one after the other: fp32 rounding grows with the length of the sum
+        parity.assert_grad_close(out.cpu().numpy(), og, 1e-5 if n <= 4096 else 1e-4, what="hub %d" % n)
 
 
 def test_gravnet_training_step_is_bit_reproducible_with_sorted_segment_backwards():
