@@ -36,6 +36,7 @@ KERNELS_PUBLISH_STATUS = 1   # the wrapper's status check after the grid build
 KERNELS_SEARCH = 2             # k_knn + k_knn_hard (the queries that gave up their walk)
 KERNELS_KNN_BWD = 1
 KERNELS_KNN_BWD_SORTED = 7   # reverse graph (6) + gather (1)
+KERNELS_GRAVNET_PROJECT = 2    # forward + backward of the fused input projections
 KERNELS_GRAVNET_FWD = 1
 KERNELS_GRAVNET_BWD = 1
 KERNELS_OC_PREPARE = 8          # + the radix sort's own kernels
@@ -122,6 +123,12 @@ SIGNATURES = {
                                    c_void_p]),
     "fgc_select_with_default": (ctypes.c_int, [c_void_p, c_i64, c_void_p, c_i64, c_i64, c_i32, c_void_p,
                                                c_void_p, c_void_p]),
+    "fgc_gravnet_project_supported": (ctypes.c_int, [c_i32, c_i32, c_i32]),
+    "fgc_gravnet_project_fwd": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_i32, c_i32, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_void_p, c_void_p, c_void_p]),
+    "fgc_gravnet_project_bwd": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_i32, c_i32, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_void_p]),
     "fgc_pyg_workspace_bytes": (c_size, [c_i64]),
     "fgc_row_splits_from_strict_batch": (ctypes.c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_size, c_void_p]),
     "fgc_pyg_read_count": (ctypes.c_int, [c_void_p, ctypes.POINTER(c_i64), c_void_p]),

@@ -55,6 +55,42 @@ def gravnet_aggregate(propagate: torch.Tensor, neighbor_idx: torch.Tensor, dists
         return _GravNetAggregate.apply(propagate, neighbor_idx, distsq, order)
 
 
+class _GravNetProject(torch.autograd.Function):
+    """Eager-mode autograd node of the fused input projections (fgc_b200::gravnet_project is its
+    dispatcher twin)."""
+
+    @staticmethod
+    def forward(ctx, x, w_space, b_space, w_prop, b_prop):
+        space, prop = torch_ops.gravnet_project_eager(x, w_space, b_space, w_prop, b_prop)
+        ctx.save_for_backward(x, w_space, w_prop)
+        ctx.has_bias = (b_space is not None, b_prop is not None)
+        ctx.set_materialize_grads(False)
+        return space, prop
+
+    @staticmethod
+    def backward(ctx, d_space, d_prop):
+        x, w_space, w_prop = ctx.saved_tensors
+        need_dx = ctx.needs_input_grad[0]
+        dx, dws, dbs, dwp, dbp = torch_ops.gravnet_project_backward_eager(x, w_space, w_prop, d_space, d_prop, need_dx)
+        return (dx if need_dx else None, dws, dbs if ctx.has_bias[0] else None, dwp,
+                dbp if ctx.has_bias[1] else None)
+
+
+def gravnet_project(x: torch.Tensor, w_space: torch.Tensor, b_space: Optional[torch.Tensor],
+                    w_prop: torch.Tensor, b_prop: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The two input projections of a GravNet layer, (x @ w_space^T + b_space, x @ w_prop^T + b_prop)
+    (gnn_ops.py:79-82 of the reference), computed in one pass over x, with a fused backward that
+    reads x and the two output gradients once.  Differentiable w.r.t. all five arguments."""
+    if torch.jit.is_scripting():
+        space, prop = torch.ops.fgc_b200.gravnet_project(x, w_space, b_space, w_prop, b_prop)
+        return space, prop
+    else:
+        if torch.jit.is_tracing() or torch.compiler.is_compiling():
+            space, prop = torch.ops.fgc_b200.gravnet_project(x, w_space, b_space, w_prop, b_prop)
+            return space, prop
+        return _GravNetProject.apply(x, w_space, b_space, w_prop, b_prop)
+
+
 class GravNetOp(torch.nn.Module):
     """One GravNet layer [arxiv:1902.07987]: learned coordinates, kNN, distance-weighted
     mean/max message passing, output transformation.
@@ -83,8 +119,11 @@ class GravNetOp(torch.nn.Module):
 
     def forward(self, x: torch.Tensor, row_splits: torch.Tensor
                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-        space = self.space_transformations(x)
-        propagate = self.propagate_transformations(x)
+        # both projections in one pass over x; the parameters stay in the two Linear modules
+        # (state_dict as in the reference)
+        space, propagate = gravnet_project(x, self.space_transformations.weight, self.space_transformations.bias,
+                                           self.propagate_transformations.weight,
+                                           self.propagate_transformations.bias)
         neighbor_idx, distsq, order = binned_select_knn_with_order(self.k, space.contiguous(), row_splits)
         fmean, fmax = gravnet_aggregate(propagate, neighbor_idx, distsq, order)
         out = self.output_transformations(torch.cat([x, fmean, fmax], dim=1))

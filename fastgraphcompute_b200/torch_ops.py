@@ -191,6 +191,105 @@ def _agg_grad(ctx, g_mean, g_max, g_argmax):
 gravnet_aggregate.register_autograd(_agg_grad, setup_context=_agg_setup)
 
 
+# --------------------------------------------------------------------------- GravNet input projections
+
+def _project_fused_ok(x: Tensor, w_space: Tensor, w_prop: Tensor) -> bool:
+    return bool(x.is_cuda and x.dim() == 2 and x.dtype == torch.float32 and w_space.dtype == torch.float32
+                and w_prop.dtype == torch.float32
+                and _cabi.lib.fgc_gravnet_project_supported(x.shape[1], w_space.shape[0], w_prop.shape[0]))
+
+
+def gravnet_project_eager(x: Tensor, w_space: Tensor, b_space: Optional[Tensor], w_prop: Tensor,
+                          b_prop: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+    """(space, propagate) = (x @ w_space^T + b_space, x @ w_prop^T + b_prop) in one pass over x; shapes
+    the fused kernel does not take go to the library GEMMs."""
+    if not _project_fused_ok(x, w_space, w_prop):
+        return (torch.nn.functional.linear(x, w_space, b_space), torch.nn.functional.linear(x, w_prop, b_prop))
+    x = x.contiguous()
+    w_space = w_space.contiguous()
+    w_prop = w_prop.contiguous()
+    n, C = x.shape
+    S, P = w_space.shape[0], w_prop.shape[0]
+    space = torch.empty((n, S), dtype=torch.float32, device=x.device)
+    prop = torch.empty((n, P), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _cabi.check(_cabi.lib.fgc_gravnet_project_fwd(
+            _cabi.ptr(x), n, C, S, P, _cabi.ptr(w_space), _cabi.ptr(None if b_space is None else b_space.contiguous()),
+            _cabi.ptr(w_prop), _cabi.ptr(None if b_prop is None else b_prop.contiguous()), _cabi.ptr(space),
+            _cabi.ptr(prop), _cabi.current_stream(x.device)), "fgc_gravnet_project_fwd")
+    return space, prop
+
+
+def gravnet_project_backward_eager(x: Tensor, w_space: Tensor, w_prop: Tensor, d_space: Optional[Tensor],
+                                   d_prop: Optional[Tensor], need_dx: bool
+                                   ) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    """(dx, dw_space, db_space, dw_prop, db_prop); dx is an empty tensor when need_dx is false."""
+    n, C = x.shape
+    S, P = w_space.shape[0], w_prop.shape[0]
+    # (the fused kernel adds the CTAs' shares of the weight gradients with float atomics: with the
+    # reproducible backward passes switched on, the library GEMMs take over)
+    if not _project_fused_ok(x, w_space, w_prop) or deterministic_gravnet_backward:
+        ds = d_space if d_space is not None else x.new_zeros((n, S))
+        dp = d_prop if d_prop is not None else x.new_zeros((n, P))
+        dx = ds @ w_space + dp @ w_prop if need_dx else x.new_empty((0,))
+        return dx, ds.t() @ x, ds.sum(0), dp.t() @ x, dp.sum(0)
+    x = x.contiguous()
+    ds = None if d_space is None else d_space.to(torch.float32).contiguous()
+    dp = None if d_prop is None else d_prop.to(torch.float32).contiguous()
+    dx = torch.empty_like(x) if need_dx else x.new_empty((0,))
+    dws = torch.empty_like(w_space, memory_format=torch.contiguous_format)
+    dwp = torch.empty_like(w_prop, memory_format=torch.contiguous_format)
+    dbs = torch.empty((S,), dtype=torch.float32, device=x.device)
+    dbp = torch.empty((P,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _cabi.check(_cabi.lib.fgc_gravnet_project_bwd(
+            _cabi.ptr(x), n, C, S, P, _cabi.ptr(w_space.contiguous()), _cabi.ptr(w_prop.contiguous()), _cabi.ptr(ds),
+            _cabi.ptr(dp), _cabi.ptr(dx) if need_dx else None, _cabi.ptr(dws), _cabi.ptr(dbs), _cabi.ptr(dwp),
+            _cabi.ptr(dbp), _cabi.current_stream(x.device)), "fgc_gravnet_project_bwd")
+    return dx, dws, dbs, dwp, dbp
+
+
+@torch.library.custom_op("fgc_b200::gravnet_project", mutates_args=())
+def gravnet_project(x: Tensor, w_space: Tensor, b_space: Optional[Tensor], w_prop: Tensor,
+                    b_prop: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+    return gravnet_project_eager(x, w_space, b_space, w_prop, b_prop)
+
+
+@gravnet_project.register_fake
+def _(x, w_space, b_space, w_prop, b_prop):
+    return (x.new_empty((x.shape[0], w_space.shape[0])), x.new_empty((x.shape[0], w_prop.shape[0])))
+
+
+@torch.library.custom_op("fgc_b200::gravnet_project_backward", mutates_args=())
+def gravnet_project_backward(x: Tensor, w_space: Tensor, w_prop: Tensor, d_space: Optional[Tensor],
+                             d_prop: Optional[Tensor], need_dx: bool
+                             ) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
+    return gravnet_project_backward_eager(x, w_space, w_prop, d_space, d_prop, need_dx)
+
+
+@gravnet_project_backward.register_fake
+def _(x, w_space, w_prop, d_space, d_prop, need_dx):
+    return (torch.empty_like(x) if need_dx else x.new_empty((0,)), torch.empty_like(w_space),
+            w_space.new_empty((w_space.shape[0],)), torch.empty_like(w_prop), w_prop.new_empty((w_prop.shape[0],)))
+
+
+def _project_setup(ctx, inputs, output):
+    x, w_space, b_space, w_prop, b_prop = inputs
+    ctx.save_for_backward(x, w_space, w_prop)
+    ctx.has_bias = (b_space is not None, b_prop is not None)
+
+
+def _project_grad(ctx, d_space, d_prop):
+    x, w_space, w_prop = ctx.saved_tensors
+    dx, dws, dbs, dwp, dbp = torch.ops.fgc_b200.gravnet_project_backward(x, w_space, w_prop, d_space, d_prop,
+                                                                         ctx.needs_input_grad[0])
+    return (dx if ctx.needs_input_grad[0] else None, dws, dbs if ctx.has_bias[0] else None, dwp,
+            dbp if ctx.has_bias[1] else None)
+
+
+gravnet_project.register_autograd(_project_grad, setup_context=_project_setup)
+
+
 # --------------------------------------------------------------------------- index_replacer, binning
 
 @torch.library.custom_op("fgc_b200::index_replacer", mutates_args=())

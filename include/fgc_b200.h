@@ -416,6 +416,30 @@ int fgc_select_with_default(const int64_t *idx, int64_t n_idx, const void *feat,
                             void *out, fgc_stream_t stream);
 
 /*
+ * The two input projections of a GravNet layer in one pass over x
+ * (fastgraphcompute/gnn_ops.py:79-82: space = Linear(C -> S)(x), propagate = Linear(C -> P)(x),
+ * two library GEMMs in the reference; their autograd backward is six more GEMMs / reductions):
+ *   fwd: out_space[n,S] = x @ w_space^T + b_space, out_prop[n,P] = x @ w_prop^T + b_prop
+ *   bwd: dx[n,C] = d_space @ w_space + d_prop @ w_prop   (skipped when dx_or_null is NULL),
+ *        dw_space[S,C], db_space[S], dw_prop[P,C], db_prop[P] (overwritten; db pointers may be
+ *        NULL); a NULL d_space / d_prop counts as zeros.
+ * x [n,C] fp32 row-major, weights [out,in] as in torch.nn.Linear.  Supported shapes: C one of
+ * 16, 32, 48, 64, 96, 128 and S + P <= 64 (fgc_gravnet_project_supported; FGC_ERR_UNSUPPORTED_DIM otherwise -- the Python
+ * layer then uses the library GEMMs).  fp32 with fused multiply-adds; the weight gradients are
+ * accumulated with float atomics across CTAs (sums of n terms: equal to a GEMM's to rounding).
+ */
+int fgc_gravnet_project_supported(int32_t n_in, int32_t n_space, int32_t n_prop);
+int fgc_gravnet_project_fwd(const float *x, int64_t n_rows, int32_t n_in, int32_t n_space, int32_t n_prop,
+                            const float *w_space, const float *b_space_or_null, const float *w_prop,
+                            const float *b_prop_or_null, float *out_space, float *out_prop,
+                            fgc_stream_t stream);
+int fgc_gravnet_project_bwd(const float *x, int64_t n_rows, int32_t n_in, int32_t n_space, int32_t n_prop,
+                            const float *w_space, const float *w_prop, const float *d_space_or_null,
+                            const float *d_prop_or_null, float *dx_or_null, float *dw_space,
+                            float *db_space_or_null, float *dw_prop, float *db_prop_or_null,
+                            fgc_stream_t stream);
+
+/*
  * Conversions between row splits and PyTorch-Geometric style batch vectors on the device
  * (fastgraphcompute/torch_geometric_interface.py:4-42 row_splits_from_strict_batch and :45-74
  * strict_batch_from_row_splits of the reference, which use nonzero / repeat_interleave).

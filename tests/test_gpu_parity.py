@@ -534,6 +534,40 @@ def test_gravnet_aggregate_vs_oracle():
         assert torch.equal(fmean2, fmean.detach()) and torch.equal(fmax2, fmax.detach())
 
 
+def test_gravnet_input_projections_vs_library_gemms():
+    """The fused input projections (one pass over x forward, one backward) against the two
+    torch.nn.functional.linear calls and their autograd, for the benchmark shape, odd shapes, the
+    largest supported shape, row counts around the tile size, an input without gradient and a
+    shape the kernel does not take (which must fall through to the library GEMMs)."""
+    from fastgraphcompute_b200.gnn_ops import gravnet_project
+    g = torch.Generator().manual_seed(31)
+    for n, C, S, P, x_grad in ((5000, 64, 4, 32, True), (1000, 12, 3, 8, True), (63, 7, 2, 3, True),
+                               (1, 8, 2, 2, True), (4097, 128, 5, 59, True), (700, 64, 4, 32, False),
+                               (300, 200, 4, 32, True)):
+        x = torch.randn((n, C), generator=g).to(DEV).requires_grad_(x_grad)
+        ws = (0.3 * torch.randn((S, C), generator=g)).to(DEV).requires_grad_(True)
+        bs = torch.randn((S,), generator=g).to(DEV).requires_grad_(True)
+        wp = (0.3 * torch.randn((P, C), generator=g)).to(DEV).requires_grad_(True)
+        bp = torch.randn((P,), generator=g).to(DEV).requires_grad_(True)
+        gs = torch.randn((n, S), generator=g).to(DEV)
+        gp = torch.randn((n, P), generator=g).to(DEV)
+        space, prop = gravnet_project(x, ws, bs, wp, bp)
+        inputs = ([x] if x_grad else []) + [ws, bs, wp, bp]
+        mine = torch.autograd.grad([space, prop], inputs, [gs, gp])
+        rs_, rp_ = torch.nn.functional.linear(x, ws, bs), torch.nn.functional.linear(x, wp, bp)
+        ref = torch.autograd.grad([rs_, rp_], inputs, [gs, gp])
+        what = "project n=%d C=%d S=%d P=%d" % (n, C, S, P)
+        parity.assert_grad_close(space.detach().cpu().numpy(), rs_.detach().cpu().numpy(), 1e-5, what + " space")
+        parity.assert_grad_close(prop.detach().cpu().numpy(), rp_.detach().cpu().numpy(), 1e-5, what + " prop")
+        for a, b, nm in zip(mine, ref, (["dx"] if x_grad else []) + ["dws", "dbs", "dwp", "dbp"]):
+            parity.assert_grad_close(a.cpu().numpy(), b.cpu().numpy(), 2e-5, what + " " + nm)
+        # only one of the two outputs used downstream: the other gradient counts as zero
+        space2, prop2 = gravnet_project(x, ws, bs, wp, bp)
+        only = torch.autograd.grad(prop2, [wp, ws], gp)
+        parity.assert_grad_close(only[0].cpu().numpy(), ref[-2].cpu().numpy(), 2e-5, what + " dwp alone")
+        assert float(only[1].abs().max()) == 0.0
+
+
 def test_gravnet_module_golden(golden_dir):
     """GravNetOp against outputs and gradients recorded from the reference module on CPU."""
     for name, c in load(golden_dir, "gravnet").items():
