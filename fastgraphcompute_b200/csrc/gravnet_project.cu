@@ -143,7 +143,7 @@ k_project_fwd(const float *__restrict__ x, long long n_rows, ProjShape h, const 
 // global gradients with one atomic per element and CTA.
 // KO = OP / 16, KC = C / 16.
 template <int KO, int KC>
-__global__ void __launch_bounds__(kProjThreads)
+__global__ void __launch_bounds__(kProjThreads, (KO * KC <= 12 ? 2 : 1))
 k_project_bwd(const float *__restrict__ x, long long n_rows, ProjShape h, const float *__restrict__ Ws,
               const float *__restrict__ Wp, const float *__restrict__ d_space, const float *__restrict__ d_prop,
               float *__restrict__ dX, float *__restrict__ dWs, float *__restrict__ dbs,
@@ -308,7 +308,8 @@ extern "C" int fgc_gravnet_project_fwd(const float *x, int64_t n_rows, int32_t n
     const size_t smem = proj_smem_bytes(h, false);
     cudaStream_t s = (cudaStream_t)stream;
     const long long n_tiles = (n_rows + kProjRows - 1) / kProjRows;
-    long long blocks = (long long)fgc::sm_count() * 3;
+    // persistent CTAs: as many as fit on the SMs (about 50 registers, 46 KB of shared memory at C = 64)
+    long long blocks = (long long)fgc::sm_count() * (smem <= 54 * 1024 ? 4 : (smem <= 72 * 1024 ? 3 : 2));
     if (blocks > n_tiles) blocks = n_tiles;
 #define FGC_PROJ_FWD(V)                                                                                      \
     do {                                                                                                     \
@@ -349,7 +350,9 @@ extern "C" int fgc_gravnet_project_bwd(const float *x, int64_t n_rows, int32_t n
     const ProjShape h = proj_shape(n_in, n_space, n_prop);
     const size_t smem = proj_smem_bytes(h, true);
     const long long n_tiles = (n_rows + kProjRows - 1) / kProjRows;
-    long long blocks = (long long)fgc::sm_count() * (smem <= 72 * 1024 ? 3 : (smem <= 110 * 1024 ? 2 : 1));
+    // persistent CTAs: two per SM (about 128 registers per thread), one where the tiles need more
+    // than half of the SM's shared memory
+    long long blocks = (long long)fgc::sm_count() * (smem <= 110 * 1024 ? 2 : 1);
     if (blocks > n_tiles) blocks = n_tiles;
 #define FGC_PROJ_BWD(V, Q)                                                                                   \
     do {                                                                                                     \
