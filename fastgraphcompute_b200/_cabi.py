@@ -114,6 +114,14 @@ SIGNATURES = {
     "fgc_gravnet_aggregate_bwd_sorted": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                         c_void_p, c_i64, c_i32, c_i32, c_void_p, c_size,
                                                         c_void_p, c_void_p, c_void_p, c_void_p]),
+    "fgc_gravnet_aggregate_fwd_ld": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_i64, c_i32, c_i32,
+                                                    c_void_p, c_void_p, c_i64, c_void_p, c_void_p, c_void_p]),
+    "fgc_gravnet_aggregate_bwd_ld": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                    c_void_p, c_i64, c_i64, c_i32, c_i32, c_void_p, c_void_p,
+                                                    c_void_p, c_void_p]),
+    "fgc_gravnet_aggregate_bwd_sorted_ld": (ctypes.c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                           c_void_p, c_i64, c_i64, c_i32, c_i32, c_void_p, c_size,
+                                                           c_void_p, c_void_p, c_void_p, c_void_p]),
     "fgc_knn_cell_order": (c_void_p, [c_void_p, c_i64, c_i32, c_i64, c_i32]),
     "fgc_knn_radius_filter": (ctypes.c_int, [c_void_p, c_void_p, c_i64, c_i32, ctypes.c_double, c_i32, c_void_p]),
     "fgc_oc_workspace_bytes": (c_size, [c_i64]),

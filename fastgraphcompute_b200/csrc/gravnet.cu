@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(kGravWarps * 32)
 k_gravnet_fwd(const float *__restrict__ prop, const int64_t *__restrict__ idx,
               const float *__restrict__ distsq, int n_vert, int K, int P,
               float *__restrict__ out_mean, float *__restrict__ out_max,
-              int32_t *__restrict__ out_argmax, const int32_t *__restrict__ order)
+              int32_t *__restrict__ out_argmax, const int32_t *__restrict__ order, int ldo)
 {
     const int lane = threadIdx.x & 31;
     const int wi = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
@@ -70,8 +70,8 @@ k_gravnet_fwd(const float *__restrict__ prop, const int64_t *__restrict__ idx,
     for (int c = 0; c < PC; c++) {
         const int p = pbase + 32 * c;
         if (p < P) {
-            out_mean[(size_t)i * P + p] = __fdiv_rn(sum[c], (float)K);
-            out_max[(size_t)i * P + p] = mx[c];
+            out_mean[(size_t)i * ldo + p] = __fdiv_rn(sum[c], (float)K);
+            out_max[(size_t)i * ldo + p] = mx[c];
             if (out_argmax) out_argmax[(size_t)i * P + p] = am[c];
         }
     }
@@ -83,7 +83,7 @@ k_gravnet_bwd(const float *__restrict__ prop, const int64_t *__restrict__ idx,
               const float *__restrict__ distsq, const int32_t *__restrict__ argmax,
               const float *__restrict__ g_mean, const float *__restrict__ g_max, int n_vert,
               int K, int P, float *__restrict__ d_prop, float *__restrict__ d_distsq,
-              int accumulate_dd, const int32_t *__restrict__ order)
+              int accumulate_dd, const int32_t *__restrict__ order, int ldg)
 {
     const int lane = threadIdx.x & 31;
     const int wi = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
@@ -96,8 +96,8 @@ k_gravnet_bwd(const float *__restrict__ prop, const int64_t *__restrict__ idx,
     for (int c = 0; c < PC; c++) {
         const int p = pbase + 32 * c;
         const bool ok = p < P;
-        gm[c] = ok ? __fdiv_rn(g_mean[(size_t)i * P + p], (float)K) : 0.f;
-        gx[c] = ok ? g_max[(size_t)i * P + p] : 0.f;
+        gm[c] = ok ? __fdiv_rn(g_mean[(size_t)i * ldg + p], (float)K) : 0.f;
+        gx[c] = ok ? g_max[(size_t)i * ldg + p] : 0.f;
         am[c] = ok ? argmax[(size_t)i * P + p] : -1;
     }
     for (int k0 = 0; k0 < K; k0 += 32) {
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(kGravWarps * 32)
 k_gravnet_fwd_v4(const float *__restrict__ prop, const int64_t *__restrict__ idx,
                  const float *__restrict__ distsq, int n_vert, int K, int P,
                  float *__restrict__ out_mean, float *__restrict__ out_max,
-                 int32_t *__restrict__ out_argmax, const int32_t *__restrict__ order)
+                 int32_t *__restrict__ out_argmax, const int32_t *__restrict__ order, int ldo)
 {
     constexpr int G = 32 / LPN;
     const int lane = threadIdx.x & 31;
@@ -201,9 +201,9 @@ k_gravnet_fwd_v4(const float *__restrict__ prop, const int64_t *__restrict__ idx
     }
     if (grp == 0 && chan) {
         const float kf = (float)K;
-        *(float4 *)(out_mean + (size_t)i * P + c4) =
+        *(float4 *)(out_mean + (size_t)i * ldo + c4) =
             make_float4(__fdiv_rn(sum[0], kf), __fdiv_rn(sum[1], kf), __fdiv_rn(sum[2], kf), __fdiv_rn(sum[3], kf));
-        *(float4 *)(out_max + (size_t)i * P + c4) = make_float4(mx[0], mx[1], mx[2], mx[3]);
+        *(float4 *)(out_max + (size_t)i * ldo + c4) = make_float4(mx[0], mx[1], mx[2], mx[3]);
         if (out_argmax) *(int4 *)(out_argmax + (size_t)i * P + c4) = make_int4(am[0], am[1], am[2], am[3]);
     }
 }
@@ -214,7 +214,7 @@ k_gravnet_bwd_v4(const float *__restrict__ prop, const int64_t *__restrict__ idx
                  const float *__restrict__ distsq, const int32_t *__restrict__ argmax,
                  const float *__restrict__ g_mean, const float *__restrict__ g_max, int n_vert,
                  int K, int P, float *__restrict__ d_prop, float *__restrict__ d_distsq,
-                 const int32_t *__restrict__ order)
+                 const int32_t *__restrict__ order, int ldg)
 {
     constexpr int G = 32 / LPN;
     const int lane = threadIdx.x & 31;
@@ -226,8 +226,8 @@ k_gravnet_bwd_v4(const float *__restrict__ prop, const int64_t *__restrict__ idx
     float gm[4] = {0.f, 0.f, 0.f, 0.f}, gx[4] = {0.f, 0.f, 0.f, 0.f};
     int am[4] = {-1, -1, -1, -1};
     if (chan) {
-        const float4 a = *(const float4 *)(g_mean + (size_t)i * P + c4);
-        const float4 b = *(const float4 *)(g_max + (size_t)i * P + c4);
+        const float4 a = *(const float4 *)(g_mean + (size_t)i * ldg + c4);
+        const float4 b = *(const float4 *)(g_max + (size_t)i * ldg + c4);
         const int4 m = *(const int4 *)(argmax + (size_t)i * P + c4);
         const float kf = (float)K;
         gm[0] = __fdiv_rn(a.x, kf); gm[1] = __fdiv_rn(a.y, kf); gm[2] = __fdiv_rn(a.z, kf); gm[3] = __fdiv_rn(a.w, kf);
@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(kGravWarps * 32)
 k_gravnet_dprop_sorted_v4(const float *__restrict__ distsq, const int32_t *__restrict__ argmax,
                           const float *__restrict__ g_mean, const float *__restrict__ g_max,
                           int n_vert, int K, int P, const int *__restrict__ offsets,
-                          const int *__restrict__ entries, float *__restrict__ d_prop)
+                          const int *__restrict__ entries, float *__restrict__ d_prop, int ldg)
 {
     constexpr int G = 32 / LPN;
     const int lane = threadIdx.x & 31;
@@ -296,8 +296,8 @@ k_gravnet_dprop_sorted_v4(const float *__restrict__ distsq, const int32_t *__res
             const int src = __ldg(entries + t);
             const int i = src / K, k = src - i * K;
             const float w = expf(__fmul_rn(-10.f, __ldg(distsq + src)));
-            const float4 a = __ldg((const float4 *)(g_mean + (size_t)i * P + c4));
-            const float4 b = __ldg((const float4 *)(g_max + (size_t)i * P + c4));
+            const float4 a = __ldg((const float4 *)(g_mean + (size_t)i * ldg + c4));
+            const float4 b = __ldg((const float4 *)(g_max + (size_t)i * ldg + c4));
             const int4 m = __ldg((const int4 *)(argmax + (size_t)i * P + c4));
             acc[0] += w * (__fdiv_rn(a.x, kf) + (m.x == k ? b.x : 0.f));
             acc[1] += w * (__fdiv_rn(a.y, kf) + (m.y == k ? b.y : 0.f));
@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(kGravWarps * 32)
 k_gravnet_dprop_sorted(const float *__restrict__ distsq, const int32_t *__restrict__ argmax,
                        const float *__restrict__ g_mean, const float *__restrict__ g_max, int n_vert,
                        int K, int P, const int *__restrict__ offsets,
-                       const int *__restrict__ entries, float *__restrict__ d_prop)
+                       const int *__restrict__ entries, float *__restrict__ d_prop, int ldg)
 {
     const int lane = threadIdx.x & 31;
     const int n = blockIdx.x * kGravWarps + (threadIdx.x >> 5);
@@ -331,8 +331,8 @@ k_gravnet_dprop_sorted(const float *__restrict__ distsq, const int32_t *__restri
             const int src = __ldg(entries + t);
             const int i = src / K, k = src - i * K;
             const float w = expf(__fmul_rn(-10.f, __ldg(distsq + src)));
-            acc += w * (__fdiv_rn(__ldg(g_mean + (size_t)i * P + p), kf) +
-                        (__ldg(argmax + (size_t)i * P + p) == k ? __ldg(g_max + (size_t)i * P + p) : 0.f));
+            acc += w * (__fdiv_rn(__ldg(g_mean + (size_t)i * ldg + p), kf) +
+                        (__ldg(argmax + (size_t)i * P + p) == k ? __ldg(g_max + (size_t)i * ldg + p) : 0.f));
         }
         d_prop[(size_t)n * P + p] = acc;
     }
@@ -340,14 +340,15 @@ k_gravnet_dprop_sorted(const float *__restrict__ distsq, const int32_t *__restri
 
 }  // namespace fgc
 
-extern "C" int fgc_gravnet_aggregate_fwd(const float *prop, const int64_t *idx, const float *distsq,
-                                         int64_t n_vert, int32_t K, int32_t P, float *out_mean,
-                                         float *out_max, int32_t *out_argmax,
-                                         const int32_t *order_or_null, fgc_stream_t stream)
+extern "C" int fgc_gravnet_aggregate_fwd_ld(const float *prop, const int64_t *idx, const float *distsq,
+                                            int64_t n_vert, int32_t K, int32_t P, float *out_mean,
+                                            float *out_max, int64_t ld_out, int32_t *out_argmax,
+                                            const int32_t *order_or_null, fgc_stream_t stream)
 {
     FGC_NVTX("fgc_gravnet_aggregate_fwd");
     using namespace fgc;
-    if (n_vert < 0 || K < 1 || P < 1) return FGC_ERR_BAD_ARGUMENT;
+    if (n_vert < 0 || K < 1 || P < 1 || ld_out < P || ld_out > 0x7fffffff) return FGC_ERR_BAD_ARGUMENT;
+    const int ldo = (int)ld_out;
     if (n_vert > 0x7fffffff) return FGC_ERR_TOO_LARGE;
     if (n_vert == 0) return FGC_OK;
     if (!prop || !idx || !distsq || !out_mean || !out_max) return FGC_ERR_BAD_ARGUMENT;
@@ -355,21 +356,74 @@ extern "C" int fgc_gravnet_aggregate_fwd(const float *prop, const int64_t *idx, 
     const int n = (int)n_vert;
     const int T = kGravWarps * 32;
     dim3 grid((unsigned)((n + kGravWarps - 1) / kGravWarps), 1);
-    const bool vec = (P % 4 == 0) && P <= 128 && (((uintptr_t)prop | (uintptr_t)out_mean | (uintptr_t)out_max |
-                                                   (uintptr_t)out_argmax) & 15) == 0;
+    const bool vec = (P % 4 == 0) && (ldo % 4 == 0) && P <= 128 &&
+                     (((uintptr_t)prop | (uintptr_t)out_mean | (uintptr_t)out_max | (uintptr_t)out_argmax) & 15) == 0;
     if (vec) {
-        if (P <= 16) k_gravnet_fwd_v4<4><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
-        else if (P <= 32) k_gravnet_fwd_v4<8><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
-        else if (P <= 64) k_gravnet_fwd_v4<16><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
-        else k_gravnet_fwd_v4<32><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
+        if (P <= 16) k_gravnet_fwd_v4<4><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null, ldo);
+        else if (P <= 32) k_gravnet_fwd_v4<8><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null, ldo);
+        else if (P <= 64) k_gravnet_fwd_v4<16><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null, ldo);
+        else k_gravnet_fwd_v4<32><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null, ldo);
         FGC_CHECK_LAUNCH();
         return FGC_OK;
     }
-    if (P <= 32) k_gravnet_fwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
-    else if (P <= 64) k_gravnet_fwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
+    if (P <= 32) k_gravnet_fwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null, ldo);
+    else if (P <= 64) k_gravnet_fwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null, ldo);
     else {
         grid.y = (unsigned)((P + 127) / 128);
-        k_gravnet_fwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null);
+        k_gravnet_fwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, n, K, P, out_mean, out_max, out_argmax, order_or_null, ldo);
+    }
+    FGC_CHECK_LAUNCH();
+    return FGC_OK;
+}
+
+extern "C" int fgc_gravnet_aggregate_fwd(const float *prop, const int64_t *idx, const float *distsq,
+                                         int64_t n_vert, int32_t K, int32_t P, float *out_mean,
+                                         float *out_max, int32_t *out_argmax,
+                                         const int32_t *order_or_null, fgc_stream_t stream)
+{
+    return fgc_gravnet_aggregate_fwd_ld(prop, idx, distsq, n_vert, K, P, out_mean, out_max, P, out_argmax,
+                                        order_or_null, stream);
+}
+
+extern "C" int fgc_gravnet_aggregate_bwd_ld(const float *prop, const int64_t *idx, const float *distsq,
+                                            const int32_t *argmax, const float *grad_mean,
+                                            const float *grad_max, int64_t ld_grad, int64_t n_vert,
+                                            int32_t K, int32_t P, float *out_d_prop, float *out_d_distsq,
+                                            const int32_t *order_or_null, fgc_stream_t stream)
+{
+    FGC_NVTX("fgc_gravnet_aggregate_bwd");
+    using namespace fgc;
+    if (n_vert < 0 || K < 1 || P < 1 || ld_grad < P || ld_grad > 0x7fffffff) return FGC_ERR_BAD_ARGUMENT;
+    const int ldg = (int)ld_grad;
+    if (n_vert > 0x7fffffff) return FGC_ERR_TOO_LARGE;
+    if (n_vert == 0) return FGC_OK;
+    if (!prop || !idx || !distsq || !argmax || !grad_mean || !grad_max || !out_d_prop || !out_d_distsq)
+        return FGC_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int n = (int)n_vert;
+    const int T = kGravWarps * 32;
+    FGC_RETURN_IF_CUDA(cudaMemsetAsync(out_d_prop, 0, sizeof(float) * (size_t)n_vert * P, s));
+    dim3 grid((unsigned)((n + kGravWarps - 1) / kGravWarps), 1);
+    const bool vec = (P % 4 == 0) && (ldg % 4 == 0) && P <= 128 &&
+                     (((uintptr_t)prop | (uintptr_t)grad_mean | (uintptr_t)grad_max | (uintptr_t)argmax |
+                       (uintptr_t)out_d_prop) & 15) == 0;
+    if (vec) {
+        if (P <= 16) k_gravnet_bwd_v4<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null, ldg);
+        else if (P <= 32) k_gravnet_bwd_v4<8><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null, ldg);
+        else if (P <= 64) k_gravnet_bwd_v4<16><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null, ldg);
+        else k_gravnet_bwd_v4<32><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null, ldg);
+        FGC_CHECK_LAUNCH();
+        return FGC_OK;
+    }
+    if (P <= 32)
+        k_gravnet_bwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, 0, order_or_null, ldg);
+    else if (P <= 64)
+        k_gravnet_bwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, 0, order_or_null, ldg);
+    else {
+        grid.y = (unsigned)((P + 127) / 128);
+        const int acc = grid.y > 1;
+        if (acc) FGC_RETURN_IF_CUDA(cudaMemsetAsync(out_d_distsq, 0, sizeof(float) * (size_t)n_vert * K, s));
+        k_gravnet_bwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, acc, order_or_null, ldg);
     }
     FGC_CHECK_LAUNCH();
     return FGC_OK;
@@ -381,37 +435,55 @@ extern "C" int fgc_gravnet_aggregate_bwd(const float *prop, const int64_t *idx, 
                                          float *out_d_prop, float *out_d_distsq,
                                          const int32_t *order_or_null, fgc_stream_t stream)
 {
-    FGC_NVTX("fgc_gravnet_aggregate_bwd");
+    return fgc_gravnet_aggregate_bwd_ld(prop, idx, distsq, argmax, grad_mean, grad_max, P, n_vert, K, P,
+                                        out_d_prop, out_d_distsq, order_or_null, stream);
+}
+
+extern "C" int fgc_gravnet_aggregate_bwd_sorted_ld(const float *prop, const int64_t *idx,
+                                                   const float *distsq, const int32_t *argmax,
+                                                   const float *grad_mean, const float *grad_max,
+                                                   int64_t ld_grad, int64_t n_vert, int32_t K, int32_t P,
+                                                   const void *rgraph, size_t rgraph_bytes,
+                                                   float *out_d_prop, float *out_d_distsq,
+                                                   const int32_t *order_or_null, fgc_stream_t stream)
+{
+    FGC_NVTX("fgc_gravnet_aggregate_bwd_sorted");
     using namespace fgc;
-    if (n_vert < 0 || K < 1 || P < 1) return FGC_ERR_BAD_ARGUMENT;
-    if (n_vert > 0x7fffffff) return FGC_ERR_TOO_LARGE;
+    if (n_vert < 0 || K < 1 || P < 1 || P > 128 || ld_grad < P || ld_grad > 0x7fffffff) return FGC_ERR_BAD_ARGUMENT;
+    const int ldg = (int)ld_grad;
+    if (n_vert * (int64_t)K > 0x7fffffff) return FGC_ERR_TOO_LARGE;
+    const ReverseGraphLayout RL = reverse_graph_layout(n_vert, K);
+    if (!rgraph || rgraph_bytes < RL.total || ((uintptr_t)rgraph & 255)) return FGC_ERR_WORKSPACE;
     if (n_vert == 0) return FGC_OK;
     if (!prop || !idx || !distsq || !argmax || !grad_mean || !grad_max || !out_d_prop || !out_d_distsq)
         return FGC_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const int n = (int)n_vert;
     const int T = kGravWarps * 32;
-    FGC_RETURN_IF_CUDA(cudaMemsetAsync(out_d_prop, 0, sizeof(float) * (size_t)n_vert * P, s));
     dim3 grid((unsigned)((n + kGravWarps - 1) / kGravWarps), 1);
-    const bool vec = (P % 4 == 0) && P <= 128 && (((uintptr_t)prop | (uintptr_t)grad_mean | (uintptr_t)grad_max |
-                                                   (uintptr_t)argmax | (uintptr_t)out_d_prop) & 15) == 0;
+    const int *offsets = (const int *)((const char *)rgraph + RL.offsets);
+    const int *entries = (const int *)((const char *)rgraph + RL.entries);
+    const bool vec = (P % 4 == 0) && (ldg % 4 == 0) &&
+                     (((uintptr_t)prop | (uintptr_t)grad_mean | (uintptr_t)grad_max | (uintptr_t)argmax |
+                       (uintptr_t)out_d_prop) & 15) == 0;
+    // d_distsq: the per-row kernel without its d_prop reductions
     if (vec) {
-        if (P <= 16) k_gravnet_bwd_v4<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null);
-        else if (P <= 32) k_gravnet_bwd_v4<8><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null);
-        else if (P <= 64) k_gravnet_bwd_v4<16><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null);
-        else k_gravnet_bwd_v4<32><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, order_or_null);
-        FGC_CHECK_LAUNCH();
-        return FGC_OK;
-    }
-    if (P <= 32)
-        k_gravnet_bwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, 0, order_or_null);
-    else if (P <= 64)
-        k_gravnet_bwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, 0, order_or_null);
-    else {
-        grid.y = (unsigned)((P + 127) / 128);
-        const int acc = grid.y > 1;
-        if (acc) FGC_RETURN_IF_CUDA(cudaMemsetAsync(out_d_distsq, 0, sizeof(float) * (size_t)n_vert * K, s));
-        k_gravnet_bwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, out_d_prop, out_d_distsq, acc, order_or_null);
+        if (P <= 16) k_gravnet_bwd_v4<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null, ldg);
+        else if (P <= 32) k_gravnet_bwd_v4<8><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null, ldg);
+        else if (P <= 64) k_gravnet_bwd_v4<16><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null, ldg);
+        else k_gravnet_bwd_v4<32><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null, ldg);
+    } else if (P <= 32) k_gravnet_bwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, 0, order_or_null, ldg);
+    else if (P <= 64) k_gravnet_bwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, 0, order_or_null, ldg);
+    else k_gravnet_bwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, 0, order_or_null, ldg);
+    FGC_CHECK_LAUNCH();
+    // d_prop: gathers over the sorted reverse segments
+    if (vec) {
+        if (P <= 16) k_gravnet_dprop_sorted_v4<4><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop, ldg);
+        else if (P <= 32) k_gravnet_dprop_sorted_v4<8><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop, ldg);
+        else if (P <= 64) k_gravnet_dprop_sorted_v4<16><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop, ldg);
+        else k_gravnet_dprop_sorted_v4<32><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop, ldg);
+    } else {
+        k_gravnet_dprop_sorted<<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop, ldg);
     }
     FGC_CHECK_LAUNCH();
     return FGC_OK;
@@ -425,42 +497,7 @@ extern "C" int fgc_gravnet_aggregate_bwd_sorted(const float *prop, const int64_t
                                                 float *out_d_prop, float *out_d_distsq,
                                                 const int32_t *order_or_null, fgc_stream_t stream)
 {
-    FGC_NVTX("fgc_gravnet_aggregate_bwd_sorted");
-    using namespace fgc;
-    if (n_vert < 0 || K < 1 || P < 1 || P > 128) return FGC_ERR_BAD_ARGUMENT;
-    if (n_vert * (int64_t)K > 0x7fffffff) return FGC_ERR_TOO_LARGE;
-    const ReverseGraphLayout RL = reverse_graph_layout(n_vert, K);
-    if (!rgraph || rgraph_bytes < RL.total || ((uintptr_t)rgraph & 255)) return FGC_ERR_WORKSPACE;
-    if (n_vert == 0) return FGC_OK;
-    if (!prop || !idx || !distsq || !argmax || !grad_mean || !grad_max || !out_d_prop || !out_d_distsq)
-        return FGC_ERR_BAD_ARGUMENT;
-    cudaStream_t s = (cudaStream_t)stream;
-    const int n = (int)n_vert;
-    const int T = kGravWarps * 32;
-    dim3 grid((unsigned)((n + kGravWarps - 1) / kGravWarps), 1);
-    const int *offsets = (const int *)((const char *)rgraph + RL.offsets);
-    const int *entries = (const int *)((const char *)rgraph + RL.entries);
-    const bool vec = (P % 4 == 0) && (((uintptr_t)prop | (uintptr_t)grad_mean | (uintptr_t)grad_max |
-                                       (uintptr_t)argmax | (uintptr_t)out_d_prop) & 15) == 0;
-    // d_distsq: the per-row kernel without its d_prop reductions
-    if (vec) {
-        if (P <= 16) k_gravnet_bwd_v4<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null);
-        else if (P <= 32) k_gravnet_bwd_v4<8><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null);
-        else if (P <= 64) k_gravnet_bwd_v4<16><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null);
-        else k_gravnet_bwd_v4<32><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, order_or_null);
-    } else if (P <= 32) k_gravnet_bwd<1><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, 0, order_or_null);
-    else if (P <= 64) k_gravnet_bwd<2><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, 0, order_or_null);
-    else k_gravnet_bwd<4><<<grid, T, 0, s>>>(prop, idx, distsq, argmax, grad_mean, grad_max, n, K, P, nullptr, out_d_distsq, 0, order_or_null);
-    FGC_CHECK_LAUNCH();
-    // d_prop: gathers over the sorted reverse segments
-    if (vec) {
-        if (P <= 16) k_gravnet_dprop_sorted_v4<4><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop);
-        else if (P <= 32) k_gravnet_dprop_sorted_v4<8><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop);
-        else if (P <= 64) k_gravnet_dprop_sorted_v4<16><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop);
-        else k_gravnet_dprop_sorted_v4<32><<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop);
-    } else {
-        k_gravnet_dprop_sorted<<<grid, T, 0, s>>>(distsq, argmax, grad_mean, grad_max, n, K, P, offsets, entries, out_d_prop);
-    }
-    FGC_CHECK_LAUNCH();
-    return FGC_OK;
+    return fgc_gravnet_aggregate_bwd_sorted_ld(prop, idx, distsq, argmax, grad_mean, grad_max, P, n_vert, K, P,
+                                               rgraph, rgraph_bytes, out_d_prop, out_d_distsq, order_or_null,
+                                               stream);
 }

@@ -55,6 +55,44 @@ def gravnet_aggregate(propagate: torch.Tensor, neighbor_idx: torch.Tensor, dists
         return _GravNetAggregate.apply(propagate, neighbor_idx, distsq, order)
 
 
+class _GravNetAggregateCat(torch.autograd.Function):
+    """Eager-mode autograd node of the aggregation that writes into [x | mean | max]
+    (fgc_b200::gravnet_aggregate_cat is its dispatcher twin)."""
+
+    @staticmethod
+    def forward(ctx, x, propagate, neighbor_idx, distsq, order):
+        cat, argmax = torch_ops.gravnet_aggregate_cat_eager(x, propagate, neighbor_idx, distsq, order)
+        ctx.save_for_backward(propagate, neighbor_idx, distsq, argmax)
+        ctx.order = order
+        ctx.n_in = x.shape[1]
+        ctx.set_materialize_grads(False)
+        return cat
+
+    @staticmethod
+    def backward(ctx, g_cat):
+        if g_cat is None:
+            return None, None, None, None, None
+        prop, idx, dsq, argmax = ctx.saved_tensors
+        g_cat = g_cat.contiguous()
+        d_prop, d_dsq = torch_ops.gravnet_aggregate_cat_backward_eager(prop, idx, dsq, argmax, g_cat, ctx.order)
+        return (g_cat[:, :ctx.n_in] if ctx.needs_input_grad[0] else None), d_prop, None, d_dsq, None
+
+
+def gravnet_aggregate_cat(x: torch.Tensor, propagate: torch.Tensor, neighbor_idx: torch.Tensor,
+                          distsq: torch.Tensor, order: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """cat([x, mean, max], dim=1) of a GravNet layer (gnn_ops.py:90-106 of the reference) with the
+    aggregation kernel writing mean and max straight into their columns, and a backward that
+    reads the gradient's columns in place.  Differentiable w.r.t. x, propagate and distsq."""
+    if torch.jit.is_scripting():
+        cat, _ = torch.ops.fgc_b200.gravnet_aggregate_cat(x, propagate, neighbor_idx, distsq, order)
+        return cat
+    else:
+        if torch.jit.is_tracing() or torch.compiler.is_compiling():
+            cat, _ = torch.ops.fgc_b200.gravnet_aggregate_cat(x, propagate, neighbor_idx, distsq, order)
+            return cat
+        return _GravNetAggregateCat.apply(x, propagate, neighbor_idx, distsq, order)
+
+
 class _GravNetProject(torch.autograd.Function):
     """Eager-mode autograd node of the fused input projections (fgc_b200::gravnet_project is its
     dispatcher twin)."""
@@ -125,6 +163,6 @@ class GravNetOp(torch.nn.Module):
                                            self.propagate_transformations.weight,
                                            self.propagate_transformations.bias)
         neighbor_idx, distsq, order = binned_select_knn_with_order(self.k, space.contiguous(), row_splits)
-        fmean, fmax = gravnet_aggregate(propagate, neighbor_idx, distsq, order)
-        out = self.output_transformations(torch.cat([x, fmean, fmax], dim=1))
+        # [x | mean | max] without a concatenation pass: the aggregation writes into its columns
+        out = self.output_transformations(gravnet_aggregate_cat(x, propagate, neighbor_idx, distsq, order))
         return out, neighbor_idx, distsq, space

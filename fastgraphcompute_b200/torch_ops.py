@@ -191,6 +191,109 @@ def _agg_grad(ctx, g_mean, g_max, g_argmax):
 gravnet_aggregate.register_autograd(_agg_grad, setup_context=_agg_setup)
 
 
+# ------------------------------------------------------- aggregation written into [x | mean | max]
+
+def gravnet_aggregate_cat_eager(x: Tensor, prop: Tensor, idx: Tensor, distsq: Tensor,
+                                order: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+    """(cat, argmax): cat = [x | mean | max] as one [N, C + 2P] matrix, the aggregation kernel
+    writing its two results straight into their columns (gnn_ops.py:90-106 of the reference
+    without the separate concatenation pass)."""
+    _cabi.require_cuda(prop, "propagate")
+    prop = prop.to(torch.float32).contiguous()
+    idx = idx.to(torch.int64).contiguous()
+    distsq = distsq.to(torch.float32).contiguous()
+    if order is not None:
+        order = order.to(torch.int32).contiguous()
+    n_vert, P = prop.shape
+    C = x.shape[1]
+    K = idx.shape[1]
+    cat = torch.empty((n_vert, C + 2 * P), dtype=torch.float32, device=prop.device)
+    cat[:, :C].copy_(x)
+    argmax = torch.empty((n_vert, P), dtype=torch.int32, device=prop.device)
+    with torch.cuda.device(prop.device):
+        _cabi.check(_cabi.lib.fgc_gravnet_aggregate_fwd_ld(
+            _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(distsq), n_vert, K, P, _cabi.ptr(cat[:, C:C + P]),
+            _cabi.ptr(cat[:, C + P:]), C + 2 * P, _cabi.ptr(argmax), _cabi.ptr(order),
+            _cabi.current_stream(prop.device)), "fgc_gravnet_aggregate_fwd_ld")
+    return cat, argmax
+
+
+@torch.library.custom_op("fgc_b200::gravnet_aggregate_cat", mutates_args=())
+def gravnet_aggregate_cat(x: Tensor, prop: Tensor, idx: Tensor, distsq: Tensor,
+                          order: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+    return gravnet_aggregate_cat_eager(x, prop, idx, distsq, order)
+
+
+@gravnet_aggregate_cat.register_fake
+def _(x, prop, idx, distsq, order):
+    return (x.new_empty((x.shape[0], x.shape[1] + 2 * prop.shape[1]), dtype=torch.float32),
+            torch.empty_like(prop, dtype=torch.int32))
+
+
+def gravnet_aggregate_cat_backward_eager(prop: Tensor, idx: Tensor, distsq: Tensor, argmax: Tensor,
+                                         g_cat: Tensor, order: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+    """(d_prop, d_distsq) from the gradient of [x | mean | max]: the kernels read the mean and
+    max columns in place (row stride C + 2P), no slices are copied."""
+    prop = prop.to(torch.float32).contiguous()
+    idx = idx.to(torch.int64).contiguous()
+    distsq = distsq.to(torch.float32).contiguous()
+    g_cat = g_cat.to(torch.float32).contiguous()
+    n_vert, P = prop.shape
+    K = idx.shape[1]
+    ld = g_cat.shape[1]
+    C = ld - 2 * P
+    g_mean, g_max = g_cat[:, C:C + P], g_cat[:, C + P:]
+    d_prop = torch.empty_like(prop)
+    d_dsq = torch.empty_like(distsq)
+    argmax = argmax.contiguous()
+    with torch.cuda.device(prop.device):
+        stream = _cabi.current_stream(prop.device)
+        rg, rbytes = None, 0
+        if deterministic_gravnet_backward and P <= 128:
+            rg, rbytes = _knn.reverse_graph(idx, keep=_knn.deterministic_backward)
+        if rbytes:
+            _cabi.check(_cabi.lib.fgc_gravnet_aggregate_bwd_sorted_ld(
+                _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(distsq), _cabi.ptr(argmax), _cabi.ptr(g_mean),
+                _cabi.ptr(g_max), ld, n_vert, K, P, _cabi.ptr(rg), rbytes, _cabi.ptr(d_prop), _cabi.ptr(d_dsq),
+                _cabi.ptr(order), stream), "fgc_gravnet_aggregate_bwd_sorted_ld")
+        else:
+            _cabi.check(_cabi.lib.fgc_gravnet_aggregate_bwd_ld(
+                _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(distsq), _cabi.ptr(argmax),
+                _cabi.ptr(g_mean), _cabi.ptr(g_max), ld, n_vert, K, P, _cabi.ptr(d_prop), _cabi.ptr(d_dsq),
+                _cabi.ptr(order), stream), "fgc_gravnet_aggregate_bwd_ld")
+    return d_prop, d_dsq
+
+
+@torch.library.custom_op("fgc_b200::gravnet_aggregate_cat_backward", mutates_args=())
+def gravnet_aggregate_cat_backward(prop: Tensor, idx: Tensor, distsq: Tensor, argmax: Tensor,
+                                   g_cat: Tensor, order: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+    return gravnet_aggregate_cat_backward_eager(prop, idx, distsq, argmax, g_cat, order)
+
+
+@gravnet_aggregate_cat_backward.register_fake
+def _(prop, idx, distsq, argmax, g_cat, order):
+    return torch.empty_like(prop, dtype=torch.float32), torch.empty_like(distsq, dtype=torch.float32)
+
+
+def _agg_cat_setup(ctx, inputs, output):
+    x, prop, idx, distsq, order = inputs
+    ctx.save_for_backward(prop, idx, distsq, output[1])
+    ctx.order = order
+    ctx.n_in = x.shape[1]
+
+
+def _agg_cat_grad(ctx, g_cat, g_argmax):
+    prop, idx, distsq, argmax = ctx.saved_tensors
+    if g_cat is None:
+        return None, None, None, None, None
+    d_prop, d_dsq = torch.ops.fgc_b200.gravnet_aggregate_cat_backward(prop, idx, distsq, argmax, g_cat,
+                                                                       ctx.order)
+    return g_cat[:, :ctx.n_in], d_prop, None, d_dsq, None
+
+
+gravnet_aggregate_cat.register_autograd(_agg_cat_grad, setup_context=_agg_cat_setup)
+
+
 # --------------------------------------------------------------------------- GravNet input projections
 
 def _project_fused_ok(x: Tensor, w_space: Tensor, w_prop: Tensor) -> bool:

@@ -282,9 +282,10 @@ int fgc_binned_knn_bwd(const float *grad_distsq, const int64_t *idx, const float
 /*
  * The same with a processing order: order_or_null [n_vert] int32, a permutation of the rows
  * (fgc_knn_cell_order of the forward's workspace, copied before the workspace is reused).
- * Rows that are neighbours in space are then processed by the same CTA, which makes the
- * scattered reads and reductions local (C2: 0.10 -> 0.08 ms).  The gradient is the same up to
- * the order of the float additions.  No counterpart in the reference.
+ * Rows that are neighbours in space are then processed by the same CTA, so that consecutive
+ * warps meet the same neighbour rows in cache (a few per cent on 200 000 points, K = 32: the
+ * ids still address rows in the caller's order).  The gradient is the same up to the order
+ * of the float additions.  No counterpart in the reference.
  */
 int fgc_binned_knn_bwd_ordered(const float *grad_distsq, const int64_t *idx, const float *coords,
                                int64_t n_vert, int32_t K, int32_t n_coords,
@@ -363,6 +364,30 @@ int fgc_gravnet_aggregate_bwd_sorted(const float *prop, const int64_t *idx, cons
                                      const void *rgraph, size_t rgraph_bytes, float *out_d_prop,
                                      float *out_d_distsq, const int32_t *order_or_null,
                                      fgc_stream_t stream);
+
+/*
+ * The three aggregation calls with a row stride (in floats) for tensors that are columns of a
+ * wider row-major matrix: ld_out for out_mean / out_max (the aggregation written straight into
+ * its columns of the concatenated input [x | mean | max] of the layer's output transformation,
+ * gnn_ops.py:106-109), ld_grad for grad_mean / grad_max (the matching columns of that matrix's
+ * gradient).  ld >= P; the 16-byte vector kernels need ld % 4 == 0 and 16-byte aligned
+ * pointers, other shapes take the scalar kernels.  Everything else as in the calls above.
+ */
+int fgc_gravnet_aggregate_fwd_ld(const float *prop, const int64_t *idx, const float *distsq,
+                                 int64_t n_vert, int32_t K, int32_t P, float *out_mean,
+                                 float *out_max, int64_t ld_out, int32_t *out_argmax,
+                                 const int32_t *order_or_null, fgc_stream_t stream);
+int fgc_gravnet_aggregate_bwd_ld(const float *prop, const int64_t *idx, const float *distsq,
+                                 const int32_t *argmax, const float *grad_mean,
+                                 const float *grad_max, int64_t ld_grad, int64_t n_vert, int32_t K,
+                                 int32_t P, float *out_d_prop, float *out_d_distsq,
+                                 const int32_t *order_or_null, fgc_stream_t stream);
+int fgc_gravnet_aggregate_bwd_sorted_ld(const float *prop, const int64_t *idx, const float *distsq,
+                                        const int32_t *argmax, const float *grad_mean,
+                                        const float *grad_max, int64_t ld_grad, int64_t n_vert,
+                                        int32_t K, int32_t P, const void *rgraph,
+                                        size_t rgraph_bytes, float *out_d_prop, float *out_d_distsq,
+                                        const int32_t *order_or_null, fgc_stream_t stream);
 
 /*
  * Radius mode of the reference's brute-force op select_knn::select_knn(coords, row_splits, mask,

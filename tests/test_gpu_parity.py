@@ -534,6 +534,45 @@ def test_gravnet_aggregate_vs_oracle():
         assert torch.equal(fmean2, fmean.detach()) and torch.equal(fmax2, fmax.detach())
 
 
+def test_gravnet_aggregate_into_concatenated_matrix():
+    """[x | mean | max] written by the aggregation kernel against torch.cat of the separate call:
+    identical values forward; the backward reads the gradient's columns in place and must give what
+    the separate call gives on copied slices (vector kernels, scalar kernels for widths that are
+    not multiples of four, wide P, both backward forms)."""
+    from fastgraphcompute_b200 import torch_ops
+    from fastgraphcompute_b200.gnn_ops import gravnet_aggregate_cat
+    g = torch.Generator().manual_seed(5)
+    for n, k, p, c in ((600, 12, 32, 64), (500, 40, 10, 7), (300, 9, 64, 12), (257, 8, 150, 5), (64, 5, 4, 4)):
+        x = torch.randn((n, c), generator=g).to(DEV).requires_grad_(True)
+        prop = torch.randn((n, p), generator=g).to(DEV).requires_grad_(True)
+        dsq = (torch.rand((n, k), generator=g) * 0.2).to(DEV).requires_grad_(True)
+        idx = torch.randint(0, n, (n, k), generator=g)
+        idx[torch.rand((n, k), generator=g) < 0.1] = -1
+        idx = idx.to(DEV)
+        gc = torch.randn((n, c + 2 * p), generator=g).to(DEV)
+        order = torch.randperm(n, generator=g).to(torch.int32).to(DEV)
+        fmean, fmax = gravnet_aggregate(prop, idx, dsq, order)
+        ref = torch.cat([x, fmean, fmax], dim=1)
+        (ref * gc).sum().backward()
+        want = [t.grad.clone() for t in (x, prop, dsq)]
+        for det in (False, True):
+            for t in (x, prop, dsq):
+                t.grad = None
+            torch_ops.deterministic_gravnet_backward = det
+            try:
+                cat = gravnet_aggregate_cat(x, prop, idx, dsq, order)
+                assert cat.shape == ref.shape and torch.equal(cat, ref.detach())
+                (cat * gc).sum().backward()
+            finally:
+                torch_ops.deterministic_gravnet_backward = False
+            assert torch.equal(x.grad, want[0])
+            parity.assert_grad_close(prop.grad.cpu().numpy(), want[1].cpu().numpy(), 1e-5, "d_prop")
+            parity.assert_grad_close(dsq.grad.cpu().numpy(), want[2].cpu().numpy(), 1e-5, "d_distsq")
+    # the dispatcher op (TorchScript, torch.compile) gives the same matrix
+    cat2, _ = torch.ops.fgc_b200.gravnet_aggregate_cat(x.detach(), prop.detach(), idx, dsq.detach(), order)
+    assert torch.equal(cat2, cat.detach())
+
+
 def test_gravnet_input_projections_vs_library_gemms():
     """The fused input projections (one pass over x forward, one backward) against the two
     torch.nn.functional.linear calls and their autograd, for the benchmark shape, odd shapes, the
