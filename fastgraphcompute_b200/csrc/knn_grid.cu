@@ -586,10 +586,16 @@ extern "C" int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int3
     const int forced = n_coords == 4 ? grid_dims : 0;
     const int n_bin_dims = forced == 3 ? 3 : (n_coords < 4 ? n_coords : 4);
     // target_occupancy > 0: one fixed grid with that mean occupancy.  Otherwise: mean
-    // occupancy 2, then the density pass may shrink the cells so that a typical point sees
-    // about seen_target points in its own cell.
+    // occupancy K/21 within [1.5, 3] (measured on B200: K = 32 is fastest at 1 to 1.5, K = 64
+    // at 3 to 4, K = 128 at 2 to 3; the optimum is flat, +-2 % over a factor of two), then
+    // the density pass may shrink the cells so that a typical point sees about seen_target
+    // points in its own cell.
     const bool adaptive = !(target_occupancy > 0.f);
-    if (adaptive) target_occupancy = 2.0f;
+    if (adaptive) {
+        target_occupancy = (float)K / 21.0f;
+        if (target_occupancy < 1.5f) target_occupancy = 1.5f;
+        if (target_occupancy > 3.0f) target_occupancy = 3.0f;
+    }
     float seen_target = (float)K / 6.0f;
     if (seen_target < 4.f) seen_target = 4.f;
     const float seen_target3 = seen_target * 2.f;    // D = 4 binned in three coordinates
