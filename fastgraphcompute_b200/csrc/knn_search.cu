@@ -24,6 +24,8 @@
 // one rounding per operation.  Visiting order, grid and stopping rule are this library's
 // own; they never change which points are nearest, only which of several equidistant
 // points is kept.
+#include <type_traits>
+
 #include "knn_grid.cuh"
 #include "shell_table.cuh"
 
@@ -141,6 +143,141 @@ struct NeighbourList {
     }
 };
 
+
+// A step in which at least this many candidates pass the vote is merged into the sorted list as
+// a whole (about 150 instructions whatever the count); fewer go in one by one (about 16 each).
+// Measured on B200: 8 is best, 5 and 12 are 0.5 to 2 % slower.
+constexpr int kBulkMin = 8;
+// One stage of a bitonic network over the 32 lanes: partner lane ^ jj; the lane keeps the
+// smaller key when want_min; equal keys keep their own entry.
+__device__ __forceinline__ void cmpx(float &d, int &id, int jj, bool want_min)
+{
+    const float od = __shfl_xor_sync(FGC_FULL_MASK, d, jj);
+    const int oi = __shfl_xor_sync(FGC_FULL_MASK, id, jj);
+    const float nd = want_min ? fminf(d, od) : fmaxf(d, od);
+    if (nd != d) id = oi;
+    d = nd;
+}
+
+// ascending over the lanes
+__device__ __forceinline__ void sort32(float &d, int &id, int lane)
+{
+#pragma unroll
+    for (int k = 2; k <= 16; k <<= 1)
+#pragma unroll
+        for (int jj = k >> 1; jj > 0; jj >>= 1) cmpx(d, id, jj, ((lane & jj) != 0) == ((lane & k) != 0));
+#pragma unroll
+    for (int jj = 16; jj > 0; jj >>= 1) cmpx(d, id, jj, (lane & jj) == 0);
+}
+
+// a bitonic sequence over the lanes into ascending order
+__device__ __forceinline__ void merge_bitonic32(float &d, int &id, int lane)
+{
+#pragma unroll
+    for (int jj = 16; jj > 0; jj >>= 1) cmpx(d, id, jj, (lane & jj) == 0);
+}
+
+// The neighbour list kept in ascending order across the warp: position s = r*32 + lane holds the
+// (s+1)-th smallest distance seen so far, +inf where there is none yet.  All 32R positions are
+// kept; the list proper is the first kn of them, so tau is the entry at position kn-1.  A single
+// candidate is inserted by a shift, a step with many passing candidates by sorting them and
+// merging the sorted sequences.
+template <int R>
+struct SortedList {
+    float d[R];
+    int id[R];
+    uint32_t tau;
+
+    __device__ __forceinline__ void init(int lane, int kn)
+    {
+#pragma unroll
+        for (int r = 0; r < R; r++) { d[r] = __uint_as_float(kInfBits); id[r] = -1; }
+        tau = kn > 0 ? kInfBits : 0u;
+    }
+
+    __device__ __forceinline__ void set_tau(int kn)
+    {
+        const float src = (R == 2 && kn > 32) ? d[R - 1] : d[0];
+        tau = __float_as_uint(__shfl_sync(FGC_FULL_MASK, src, (kn - 1) & 31));
+    }
+
+    // warp-uniform candidate with dc < tau
+    __device__ __forceinline__ void insert(int lane, int kn, float dc, int jc)
+    {
+        const int p0 = __popc(__ballot_sync(FGC_FULL_MASK, d[0] <= dc));
+        if (R == 1 || p0 < 32) {
+            float c_d = 0.f; int c_i = 0;
+            if (R == 2) {
+                c_d = __shfl_sync(FGC_FULL_MASK, d[0], 31);
+                c_i = __shfl_sync(FGC_FULL_MASK, id[0], 31);
+            }
+            const float du = __shfl_up_sync(FGC_FULL_MASK, d[0], 1);
+            const int iu = __shfl_up_sync(FGC_FULL_MASK, id[0], 1);
+            if (lane > p0) { d[0] = du; id[0] = iu; }
+            else if (lane == p0) { d[0] = dc; id[0] = jc; }
+            if (R == 2) {
+                const float du1 = __shfl_up_sync(FGC_FULL_MASK, d[R - 1], 1);
+                const int iu1 = __shfl_up_sync(FGC_FULL_MASK, id[R - 1], 1);
+                d[R - 1] = lane == 0 ? c_d : du1;
+                id[R - 1] = lane == 0 ? c_i : iu1;
+            }
+        } else {
+            const int p = __popc(__ballot_sync(FGC_FULL_MASK, d[R - 1] <= dc));
+            const float du = __shfl_up_sync(FGC_FULL_MASK, d[R - 1], 1);
+            const int iu = __shfl_up_sync(FGC_FULL_MASK, id[R - 1], 1);
+            if (lane > p) { d[R - 1] = du; id[R - 1] = iu; }
+            else if (lane == p) { d[R - 1] = dc; id[R - 1] = jc; }
+        }
+        set_tau(kn);
+    }
+
+    // two ascending sequences of 32 (lo, hi) into one ascending sequence of 64
+    __device__ __forceinline__ void merge_halves(int lane)
+    {
+        float cr = __shfl_sync(FGC_FULL_MASK, d[R - 1], 31 - lane);
+        int ir = __shfl_sync(FGC_FULL_MASK, id[R - 1], 31 - lane);
+        if (cr < d[0]) {
+            const float td = d[0]; const int ti = id[0];
+            d[0] = cr; id[0] = ir; cr = td; ir = ti;
+        }
+        d[R - 1] = cr; id[R - 1] = ir;
+#pragma unroll
+        for (int jj = 16; jj > 0; jj >>= 1) {
+            cmpx(d[0], id[0], jj, (lane & jj) == 0);
+            cmpx(d[R - 1], id[R - 1], jj, (lane & jj) == 0);
+        }
+    }
+
+    // one candidate per lane (+inf where the lane has none): keep the 32R smallest of list and
+    // candidates
+    __device__ __forceinline__ void merge32(int lane, int kn, float dc, int jc)
+    {
+        sort32(dc, jc, lane);
+        const unsigned lo_has = __ballot_sync(FGC_FULL_MASK, __float_as_uint(d[0]) < kInfBits);
+        const unsigned hi_has = R == 2 ? __ballot_sync(FGC_FULL_MASK, __float_as_uint(d[R - 1]) < kInfBits) : 0u;
+        if (lo_has == 0) {
+            d[0] = dc; id[0] = jc;
+        } else if (R == 2 && hi_has == 0) {
+            // the upper half is empty: the candidates become the upper half
+            d[R - 1] = dc; id[R - 1] = jc;
+            merge_halves(lane);
+        } else {
+            // against the top 32 positions: the elementwise minimum with the reversed candidates is
+            // a bitonic sequence of the 32 smallest of the two
+            const float cr = __shfl_sync(FGC_FULL_MASK, dc, 31 - lane);
+            const int ir = __shfl_sync(FGC_FULL_MASK, jc, 31 - lane);
+            if (cr < d[R - 1]) { d[R - 1] = cr; id[R - 1] = ir; }
+            merge_bitonic32(d[R - 1], id[R - 1], lane);
+            if (R == 2) {
+                const float lo_max = __shfl_sync(FGC_FULL_MASK, d[0], 31);
+                const float hi_min = __shfl_sync(FGC_FULL_MASK, d[R - 1], 0);
+                if (hi_min < lo_max) merge_halves(lane);
+            }
+        }
+        set_tau(kn);
+    }
+};
+
 // The search of one query by one warp.  G4: the grid spans four coordinates, else three.
 template <int NV, int R, bool COUNT, bool G4>
 __device__ __forceinline__ void knn_query(const KnnArgs &a)
@@ -185,7 +322,14 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
 #pragma unroll
     for (int v = 0; v < NV; v++) q[v] = __ldg(a.scoords + (size_t)qi * NV + v);
 
-    NeighbourList<R> list;
+    // Sorted list where it was measured faster than the unordered one (B200, uniform, normal and
+    // clustered data in 3 to 8 dimensions, K = 8..64): one slot per lane (-2 to -20 %, except
+    // uniform 3-D data at K = 32, +7 %: few insertions follow the first sort there), two slots
+    // per lane with one float4 per point (-10 to -23 % for K = 40, 48; -1 to -15 % for K = 64).
+    // Two slots with more than four coordinates lose 3 to 4 % (registers), four and more slots
+    // per lane keep the unordered list.
+    constexpr bool SORTED = R == 1 || (R == 2 && NV == 1);
+    typename std::conditional<SORTED, SortedList<R>, NeighbourList<R>>::type list;
     list.init(lane, kn);
     unsigned cnt_evals = 0, cnt_steps = 0, cnt_ins = 0, cnt_batches = 0, cnt_shells = 0, cnt_brute = 0;
 
@@ -204,46 +348,53 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
         unsigned m = __ballot_sync(FGC_FULL_MASK, __float_as_uint(dc) < list.tau);
         if (m == 0) return;
         const int npass = __popc(m);
-        if (R == 1 && list.tau == kInfBits) {
-            // While the list has empty slots any of them may take a passing candidate: a lane
-            // whose own slot is empty keeps its own candidate, with no warp-wide insertion.
-            // What is left (lanes whose slot is taken or not part of the list) goes one by one.
-            const bool take = (m >> lane & 1) && __float_as_uint(list.d[0]) == kInfBits;
-            if (take) { list.d[0] = dc; list.id[0] = j; list.lmax = __float_as_uint(dc); }
-            const unsigned tm = __ballot_sync(FGC_FULL_MASK, take);
-            list.filled += __popc(tm);
-            list.tau = __reduce_max_sync(FGC_FULL_MASK, list.lmax);
-            if (COUNT) cnt_ins += __popc(tm);
-            m &= ~tm;
-        }
-        if (R >= 2 && list.filled + npass <= kn) {
-            // all passing candidates fit into empty slots (tau is +inf here): place them in
-            // one go through shared memory instead of one warp-wide insertion each (pays
-            // off once a lane holds more than one slot)
-            if (m >> lane & 1) {
-                const int rk = __popc(m & lanemask_lt());
-                s_bd[wib][rk] = dc;
-                s_bj[wib][rk] = j;
+        if constexpr (SORTED) {
+            if (npass >= kBulkMin) {
+                list.merge32(lane, kn, (m >> lane & 1) ? dc : __uint_as_float(kInfBits), j);
+                if (COUNT) cnt_ins += npass;
+                return;
             }
-            __syncwarp();
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int src = lane * R + r - list.filled;
-                if (src >= 0 && src < npass) { list.d[r] = s_bd[wib][src]; list.id[r] = s_bj[wib][src]; }
+            while (m) {
+                const int src = __ffs(m) - 1;
+                m &= m - 1;
+                const float dcs = __shfl_sync(FGC_FULL_MASK, dc, src);
+                const int js = __shfl_sync(FGC_FULL_MASK, j, src);
+                if (__float_as_uint(dcs) < list.tau) {
+                    list.insert(lane, kn, dcs, js);
+                    if (COUNT) cnt_ins += 1;
+                }
             }
-            __syncwarp();
-            list.filled += npass;
-            list.refresh(lane);
-            if (COUNT) cnt_ins += npass;
             return;
-        }
-        while (m) {
-            const int src = __ffs(m) - 1;
-            m &= m - 1;
-            const float dcs = __shfl_sync(FGC_FULL_MASK, dc, src);
-            const int js = __shfl_sync(FGC_FULL_MASK, j, src);
-            const int ins = list.offer(lane, dcs, js);
-            if (COUNT) cnt_ins += ins;
+        } else {
+            if (R >= 2 && list.filled + npass <= kn) {
+                // all passing candidates fit into empty slots (tau is +inf here): place them in
+                // one go through shared memory instead of one warp-wide insertion each (pays
+                // off once a lane holds more than one slot)
+                if (m >> lane & 1) {
+                    const int rk = __popc(m & lanemask_lt());
+                    s_bd[wib][rk] = dc;
+                    s_bj[wib][rk] = j;
+                }
+                __syncwarp();
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const int src = lane * R + r - list.filled;
+                    if (src >= 0 && src < npass) { list.d[r] = s_bd[wib][src]; list.id[r] = s_bj[wib][src]; }
+                }
+                __syncwarp();
+                list.filled += npass;
+                list.refresh(lane);
+                if (COUNT) cnt_ins += npass;
+                return;
+            }
+            while (m) {
+                const int src = __ffs(m) - 1;
+                m &= m - 1;
+                const float dcs = __shfl_sync(FGC_FULL_MASK, dc, src);
+                const int js = __shfl_sync(FGC_FULL_MASK, j, src);
+                const int ins = list.offer(lane, dcs, js);
+                if (COUNT) cnt_ins += ins;
+            }
         }
     };
 
@@ -432,17 +583,16 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
     // epilogue: original ids, original row position
     if (lane == 0) { out_i[0] = orig_q; out_d[0] = 0.f; }
     const int64_t pad = a.tf_compat ? (int64_t)orig_q : (int64_t)-1;
-    if (R == 1) {
-        // occupied slots first, empty ones after them (with one slot per lane the list fills
-        // in no particular slot order)
-        const bool valid = lane < kn;
-        const bool filled = valid && __float_as_uint(list.d[0]) < kInfBits && list.id[0] >= 0;
-        const unsigned fm = __ballot_sync(FGC_FULL_MASK, filled);
-        const unsigned em = __ballot_sync(FGC_FULL_MASK, valid && !filled);
-        const int s = filled ? __popc(fm & lanemask_lt()) : __popc(fm) + __popc(em & lanemask_lt());
-        if (valid) {
-            out_i[1 + s] = filled ? (int64_t)__ldg(a.sorig + list.id[0]) : pad;
-            out_d[1 + s] = filled ? list.d[0] : 0.f;
+    if constexpr (SORTED) {
+        // ascending distances; positions from kn on are not part of the list
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const int s = r * 32 + lane;
+            if (s < kn) {
+                const bool filled = list.d[r] < __uint_as_float(kInfBits) && list.id[r] >= 0;
+                out_i[1 + s] = filled ? (int64_t)__ldg(a.sorig + list.id[r]) : pad;
+                out_d[1 + s] = filled ? list.d[r] : 0.f;
+            }
         }
     } else {
 #pragma unroll
