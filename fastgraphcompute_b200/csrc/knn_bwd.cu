@@ -9,7 +9,10 @@
 // row's own term is reduced inside the warp and leaves as ONE add per
 // coordinate, the neighbour term leaves as one reduction per slot: a 16-byte
 // (D = 4) or 8-byte (D = 2) vector reduction, else one fp32 reduction per
-// coordinate.
+// coordinate.  (Summing the neighbour terms of 64 cell-adjacent rows per target in a
+// shared-memory hash table first, one reduction per distinct target and CTA, was measured
+// at twice the time: float adds on shared memory plus the probe cost more than the L2
+// reductions they save; without any reductions the kernel would be 22 % faster.)
 //
 // `order` (optional) is a permutation of the rows: warp w works on row order[w].  Given the
 // cell order of the search that produced idx, the warps of a CTA work on rows of one cell or of
@@ -45,10 +48,19 @@ k_knn_bwd(const float *__restrict__ grad_distsq, const int64_t *__restrict__ idx
                 const int64_t n = idx[(size_t)i * K + k];
                 if (n >= 0 && n < n_vert) {
                     const float g2 = 2.f * grad_distsq[(size_t)i * K + k];
-                    float c[DM];
+                    float c[DM], xn[DM];
+                    if (D == 4 && vec_ok) {
+                        // one 16-byte gather instead of four 4-byte ones: the kernel is bound by
+                        // L1TEX requests (C2: 0.099 -> 0.080 ms)
+                        const float4 t4 = __ldg((const float4 *)coords + n);
+                        xn[0] = t4.x; xn[1 % DM] = t4.y; xn[2 % DM] = t4.z; xn[3 % DM] = t4.w;
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < DM; v++) xn[v] = __ldg(coords + (size_t)n * nc + v);
+                    }
 #pragma unroll
                     for (int v = 0; v < DM; v++) {
-                        c[v] = g2 * (__ldg(coords + (size_t)n * nc + v) - xi[v]);
+                        c[v] = g2 * (xn[v] - xi[v]);
                         self[v] -= c[v];
                     }
                     // one vector reduction per neighbour where the row is 8 or 16 bytes wide
@@ -117,7 +129,7 @@ extern "C" int fgc_binned_knn_bwd_ordered(const float *grad_distsq, const int64_
     const int n = (int)n_vert;
     const unsigned blocks = (unsigned)((n + kBwdWarps - 1) / kBwdWarps);
     const int T = kBwdWarps * 32;
-    const int vec_ok = ((uintptr_t)out_grad_coords & 15) == 0;
+    const int vec_ok = (((uintptr_t)out_grad_coords | (uintptr_t)coords) & 15) == 0;
     switch (n_coords) {
     case 2: k_knn_bwd<2><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
     case 3: k_knn_bwd<3><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
