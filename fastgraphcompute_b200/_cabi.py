@@ -131,6 +131,11 @@ SIGNATURES = {
                                    c_void_p]),
     "fgc_select_with_default": (ctypes.c_int, [c_void_p, c_i64, c_void_p, c_i64, c_i64, c_i32, c_void_p,
                                                c_void_p, c_void_p]),
+    "fgc_gravnet_project_fwd_cat": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_i32, c_i32, c_void_p, c_void_p, c_void_p,
+                                                   c_void_p, c_void_p, c_void_p, c_void_p, c_i64, c_void_p]),
+    "fgc_gravnet_project_bwd_cat": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_i32, c_i32, c_void_p, c_void_p, c_void_p,
+                                                   c_void_p, c_void_p, c_i64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                   c_void_p, c_void_p]),
     "fgc_gravnet_project_supported": (ctypes.c_int, [c_i32, c_i32, c_i32]),
     "fgc_gravnet_project_fwd": (ctypes.c_int, [c_void_p, c_i64, c_i32, c_i32, c_i32, c_void_p, c_void_p, c_void_p,
                                                c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -51,10 +51,14 @@ inline size_t proj_smem_bytes(const ProjShape &s, bool backward)
 }
 
 // x tile, transposed: sXt[c][r] = x[row0 + r][c] (zero beyond the last row); coalesced global reads
+// copy (optional): the rows are also written to copy[row * ld_copy + c], the first `width` columns of
+// a wider row-major matrix
 __device__ __forceinline__ void proj_load_tile_t(float *sT, const float *__restrict__ src, long long row0,
-                                                 long long n_rows, int width)
+                                                 long long n_rows, int width, float *__restrict__ copy = nullptr,
+                                                 long long ld_copy = 0)
 {
-    if ((width & (width - 1)) == 0 && width >= 4 && width <= 128 && ((uintptr_t)src & 15) == 0) {
+    if ((width & (width - 1)) == 0 && width >= 4 && width <= 128 && ((uintptr_t)src & 15) == 0 &&
+        (!copy || ((((uintptr_t)copy) & 15) == 0 && (ld_copy & 3) == 0))) {
         // rows of 4, 8, ..., 128 floats: one 16-byte load per thread and pass, no divisions
         const int vpr = width >> 2;                       // 16-byte words per row (1..32)
         const int sh = 31 - __clz(vpr);
@@ -63,7 +67,10 @@ __device__ __forceinline__ void proj_load_tile_t(float *sT, const float *__restr
         for (int r = rr; r < kProjRows; r += rows_per_pass) {
             const long long row = row0 + r;
             float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (row < n_rows) val = __ldg((const float4 *)(src + (size_t)row * width) + v);
+            if (row < n_rows) {
+                val = __ldg((const float4 *)(src + (size_t)row * width) + v);
+                if (copy) *((float4 *)(copy + (size_t)row * ld_copy) + v) = val;
+            }
             float *dst = sT + (4 * v) * kProjRowsP + r;
             dst[0] = val.x;
             dst[kProjRowsP] = val.y;
@@ -76,7 +83,9 @@ __device__ __forceinline__ void proj_load_tile_t(float *sT, const float *__restr
     for (int i = threadIdx.x; i < total; i += kProjThreads) {
         const int r = i / width, c = i - r * width;
         const long long row = row0 + r;
-        sT[c * kProjRowsP + r] = row < n_rows ? __ldg(src + (size_t)row * width + c) : 0.f;
+        const float val = row < n_rows ? __ldg(src + (size_t)row * width + c) : 0.f;
+        sT[c * kProjRowsP + r] = val;
+        if (copy && row < n_rows) copy[(size_t)row * ld_copy + c] = val;
     }
 }
 
@@ -85,7 +94,8 @@ template <int KO>
 __global__ void __launch_bounds__(kProjThreads)
 k_project_fwd(const float *__restrict__ x, long long n_rows, ProjShape h, const float *__restrict__ Ws,
               const float *__restrict__ bs, const float *__restrict__ Wp, const float *__restrict__ bp,
-              float *__restrict__ out_space, float *__restrict__ out_prop)
+              float *__restrict__ out_space, float *__restrict__ out_prop, float *__restrict__ x_copy,
+              long long ld_copy)
 {
     extern __shared__ __align__(16) float proj_smem[];
     float *sW = proj_smem;                       // [C][OP]: transposed weights, a thread's outputs contiguous
@@ -104,7 +114,7 @@ k_project_fwd(const float *__restrict__ x, long long n_rows, ProjShape h, const 
     const long long n_tiles = (n_rows + kProjRows - 1) / kProjRows;
     for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         __syncthreads();
-        proj_load_tile_t(sX, x, tile * kProjRows, n_rows, h.C);
+        proj_load_tile_t(sX, x, tile * kProjRows, n_rows, h.C, x_copy, ld_copy);
         __syncthreads();
         float acc[8][KO];
 #pragma unroll
@@ -147,7 +157,8 @@ __global__ void __launch_bounds__(kProjThreads, (KO * KC <= 12 ? 2 : 1))
 k_project_bwd(const float *__restrict__ x, long long n_rows, ProjShape h, const float *__restrict__ Ws,
               const float *__restrict__ Wp, const float *__restrict__ d_space, const float *__restrict__ d_prop,
               float *__restrict__ dX, float *__restrict__ dWs, float *__restrict__ dbs,
-              float *__restrict__ dWp, float *__restrict__ dbp)
+              float *__restrict__ dWp, float *__restrict__ dbp, const float *__restrict__ dx_add,
+              long long ld_add)
 {
     extern __shared__ __align__(16) float proj_smem[];
     float *sW = proj_smem;                       // [OP][C] (row o: the C input weights of output o)
@@ -223,6 +234,13 @@ k_project_bwd(const float *__restrict__ x, long long n_rows, ProjShape h, const 
             for (int i = 0; i < 8; i++) {
                 const long long row = row0 + hi * 8 + i;
                 if (row < n_rows) {
+                    // dx_add: a second gradient of x (the x columns of the gradient of [x | mean | max])
+                    // joins here instead of in a pass of its own
+                    if (dx_add) {
+                        const float *ad = dx_add + (size_t)row * ld_add + lo * KC;
+#pragma unroll
+                        for (int j = 0; j < KC; j++) a[i][j] += __ldg(ad + j);
+                    }
                     if constexpr (KC % 4 == 0) {
 #pragma unroll
                         for (int j = 0; j < KC; j += 4)
@@ -298,9 +316,19 @@ extern "C" int fgc_gravnet_project_fwd(const float *x, int64_t n_rows, int32_t n
                                        const float *w_prop, const float *b_prop_or_null, float *out_space,
                                        float *out_prop, fgc_stream_t stream)
 {
+    return fgc_gravnet_project_fwd_cat(x, n_rows, n_in, n_space, n_prop, w_space, b_space_or_null, w_prop,
+                                       b_prop_or_null, out_space, out_prop, nullptr, 0, stream);
+}
+
+extern "C" int fgc_gravnet_project_fwd_cat(const float *x, int64_t n_rows, int32_t n_in, int32_t n_space,
+                                           int32_t n_prop, const float *w_space, const float *b_space_or_null,
+                                           const float *w_prop, const float *b_prop_or_null, float *out_space,
+                                           float *out_prop, float *x_copy_or_null, int64_t ld_copy,
+                                           fgc_stream_t stream)
+{
     FGC_NVTX("fgc_gravnet_project_fwd");
     using namespace fgc;
-    if (n_rows < 0) return FGC_ERR_BAD_ARGUMENT;
+    if (n_rows < 0 || (x_copy_or_null && ld_copy < n_in)) return FGC_ERR_BAD_ARGUMENT;
     if (!proj_supported(n_in, n_space, n_prop)) return FGC_ERR_UNSUPPORTED_DIM;
     if (n_rows == 0) return FGC_OK;
     if (!x || !w_space || !w_prop || !out_space || !out_prop) return FGC_ERR_BAD_ARGUMENT;
@@ -316,7 +344,8 @@ extern "C" int fgc_gravnet_project_fwd(const float *x, int64_t n_rows, int32_t n
         FGC_RETURN_IF_CUDA(cudaFuncSetAttribute(k_project_fwd<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                                 (int)smem));                                                 \
         k_project_fwd<V><<<(unsigned)blocks, kProjThreads, smem, s>>>(x, n_rows, h, w_space, b_space_or_null, \
-                                                                     w_prop, b_prop_or_null, out_space, out_prop); \
+                                                                     w_prop, b_prop_or_null, out_space, out_prop, \
+                                                                     x_copy_or_null, (long long)ld_copy); \
     } while (0)
     switch (h.OP / 16) {
     case 1: FGC_PROJ_FWD(1); break;
@@ -334,9 +363,21 @@ extern "C" int fgc_gravnet_project_bwd(const float *x, int64_t n_rows, int32_t n
                                        float *dx_or_null, float *dw_space, float *db_space_or_null,
                                        float *dw_prop, float *db_prop_or_null, fgc_stream_t stream)
 {
+    return fgc_gravnet_project_bwd_cat(x, n_rows, n_in, n_space, n_prop, w_space, w_prop, d_space_or_null,
+                                       d_prop_or_null, nullptr, 0, dx_or_null, dw_space, db_space_or_null,
+                                       dw_prop, db_prop_or_null, stream);
+}
+
+extern "C" int fgc_gravnet_project_bwd_cat(const float *x, int64_t n_rows, int32_t n_in, int32_t n_space,
+                                           int32_t n_prop, const float *w_space, const float *w_prop,
+                                           const float *d_space_or_null, const float *d_prop_or_null,
+                                           const float *dx_add_or_null, int64_t ld_add, float *dx_or_null,
+                                           float *dw_space, float *db_space_or_null, float *dw_prop,
+                                           float *db_prop_or_null, fgc_stream_t stream)
+{
     FGC_NVTX("fgc_gravnet_project_bwd");
     using namespace fgc;
-    if (n_rows < 0) return FGC_ERR_BAD_ARGUMENT;
+    if (n_rows < 0 || (dx_add_or_null && ld_add < n_in)) return FGC_ERR_BAD_ARGUMENT;
     if (!proj_supported(n_in, n_space, n_prop)) return FGC_ERR_UNSUPPORTED_DIM;
     if (!w_space || !w_prop || !dw_space || !dw_prop) return FGC_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
@@ -360,7 +401,7 @@ extern "C" int fgc_gravnet_project_bwd(const float *x, int64_t n_rows, int32_t n
                                                 (int)smem));                                                 \
         k_project_bwd<V, Q><<<(unsigned)blocks, kProjThreads, smem, s>>>(                                    \
             x, n_rows, h, w_space, w_prop, d_space_or_null, d_prop_or_null, dx_or_null, dw_space,            \
-            db_space_or_null, dw_prop, db_prop_or_null);                                                     \
+            db_space_or_null, dw_prop, db_prop_or_null, dx_add_or_null, (long long)ld_add);                  \
     } while (0)
 #define FGC_PROJ_BWD_KC(V)                                                                                   \
     do {                                                                                                     \

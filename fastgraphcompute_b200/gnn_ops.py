@@ -114,6 +114,81 @@ class _GravNetProject(torch.autograd.Function):
                 dbp if ctx.has_bias[1] else None)
 
 
+class _GravNetProjectCat(torch.autograd.Function):
+    """Eager-mode node: the fused input projections that also start the matrix [x | mean | max]
+    (x written into its first columns by the same pass).  Its backward takes the gradient of that
+    matrix and adds its x columns to dx inside the kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w_space, b_space, w_prop, b_prop, cat_extra):
+        space, prop, cat = torch_ops.gravnet_project_eager(x, w_space, b_space, w_prop, b_prop, cat_extra)
+        ctx.save_for_backward(x, w_space, w_prop)
+        ctx.has_bias = (b_space is not None, b_prop is not None)
+        ctx.set_materialize_grads(False)
+        return space, prop, cat
+
+    @staticmethod
+    def backward(ctx, d_space, d_prop, d_cat):
+        x, w_space, w_prop = ctx.saved_tensors
+        need_dx = ctx.needs_input_grad[0]
+        dx, dws, dbs, dwp, dbp = torch_ops.gravnet_project_backward_eager(x, w_space, w_prop, d_space, d_prop,
+                                                                          need_dx, d_cat)
+        return (dx if need_dx else None, dws, dbs if ctx.has_bias[0] else None, dwp,
+                dbp if ctx.has_bias[1] else None, None)
+
+
+class _GravNetAggregateInto(torch.autograd.Function):
+    """Eager-mode node: the aggregation writing mean and max into their columns of the matrix that
+    _GravNetProjectCat started (in place).  The gradient of the matrix passes through to that node,
+    which reads only its x columns; this node reads the mean and max columns."""
+
+    @staticmethod
+    def forward(ctx, cat, propagate, neighbor_idx, distsq, order, n_in):
+        argmax = torch_ops.gravnet_aggregate_into_eager(cat, n_in, propagate, neighbor_idx, distsq, order)
+        ctx.mark_dirty(cat)
+        ctx.save_for_backward(propagate, neighbor_idx, distsq, argmax)
+        ctx.order = order
+        ctx.set_materialize_grads(False)
+        return cat
+
+    @staticmethod
+    def backward(ctx, g_cat):
+        if g_cat is None:
+            return None, None, None, None, None, None
+        prop, idx, dsq, argmax = ctx.saved_tensors
+        g_cat = g_cat.contiguous()
+        d_prop, d_dsq = torch_ops.gravnet_aggregate_cat_backward_eager(prop, idx, dsq, argmax, g_cat, ctx.order)
+        return g_cat, d_prop, None, d_dsq, None, None
+
+
+def gravnet_project_and_aggregate(x: torch.Tensor, w_space: torch.Tensor, b_space: Optional[torch.Tensor],
+                                  w_prop: torch.Tensor, b_prop: Optional[torch.Tensor], k: int,
+                                  row_splits: torch.Tensor
+                                  ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Everything of a GravNet layer in front of its output transformation (gnn_ops.py:79-106 of the
+    reference): (cat([x, mean, max], 1), neighbor_idx, distsq, space).
+
+    In eager mode x is copied into the matrix by the projection kernel, mean and max are written
+    into it by the aggregation kernel, and the two gradients of x (through the matrix and through the
+    projections) are added inside the projection backward.  Under TorchScript, tracing and
+    torch.compile the same result comes from the dispatcher ops."""
+    if torch.jit.is_scripting():
+        space, prop = torch.ops.fgc_b200.gravnet_project(x, w_space, b_space, w_prop, b_prop)
+        neighbor_idx, distsq, order = binned_select_knn_with_order(k, space.contiguous(), row_splits)
+        cat, _ = torch.ops.fgc_b200.gravnet_aggregate_cat(x, prop, neighbor_idx, distsq, order)
+        return cat, neighbor_idx, distsq, space
+    else:
+        if torch.jit.is_tracing() or torch.compiler.is_compiling() or not x.is_cuda:
+            space, prop = gravnet_project(x, w_space, b_space, w_prop, b_prop)
+            neighbor_idx, distsq, order = binned_select_knn_with_order(k, space.contiguous(), row_splits)
+            return gravnet_aggregate_cat(x, prop, neighbor_idx, distsq, order), neighbor_idx, distsq, space
+        x = x.to(torch.float32)
+        space, prop, cat = _GravNetProjectCat.apply(x, w_space, b_space, w_prop, b_prop, 2 * w_prop.shape[0])
+        neighbor_idx, distsq, order = binned_select_knn_with_order(k, space.contiguous(), row_splits)
+        cat = _GravNetAggregateInto.apply(cat, prop, neighbor_idx, distsq, order, x.shape[1])
+        return cat, neighbor_idx, distsq, space
+
+
 def gravnet_project(x: torch.Tensor, w_space: torch.Tensor, b_space: Optional[torch.Tensor],
                     w_prop: torch.Tensor, b_prop: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
     """The two input projections of a GravNet layer, (x @ w_space^T + b_space, x @ w_prop^T + b_prop)
@@ -157,12 +232,10 @@ class GravNetOp(torch.nn.Module):
 
     def forward(self, x: torch.Tensor, row_splits: torch.Tensor
                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-        # both projections in one pass over x; the parameters stay in the two Linear modules
-        # (state_dict as in the reference)
-        space, propagate = gravnet_project(x, self.space_transformations.weight, self.space_transformations.bias,
-                                           self.propagate_transformations.weight,
-                                           self.propagate_transformations.bias)
-        neighbor_idx, distsq, order = binned_select_knn_with_order(self.k, space.contiguous(), row_splits)
-        # [x | mean | max] without a concatenation pass: the aggregation writes into its columns
-        out = self.output_transformations(gravnet_aggregate_cat(x, propagate, neighbor_idx, distsq, order))
+        # both projections in one pass over x, [x | mean | max] without a concatenation pass; the
+        # parameters stay in the Linear modules (state_dict as in the reference)
+        cat, neighbor_idx, distsq, space = gravnet_project_and_aggregate(
+            x, self.space_transformations.weight, self.space_transformations.bias,
+            self.propagate_transformations.weight, self.propagate_transformations.bias, self.k, row_splits)
+        out = self.output_transformations(cat)
         return out, neighbor_idx, distsq, space

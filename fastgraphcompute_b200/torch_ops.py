@@ -218,6 +218,30 @@ def gravnet_aggregate_cat_eager(x: Tensor, prop: Tensor, idx: Tensor, distsq: Te
     return cat, argmax
 
 
+def gravnet_aggregate_into_eager(cat: Tensor, n_in: int, prop: Tensor, idx: Tensor, distsq: Tensor,
+                                 order: Optional[Tensor]) -> Tensor:
+    """Writes mean and max into columns n_in.. of cat ([N, n_in + 2P], row-major) in place and
+    returns the argmax tensor."""
+    _cabi.require_cuda(prop, "propagate")
+    prop = prop.to(torch.float32).contiguous()
+    idx = idx.to(torch.int64).contiguous()
+    distsq = distsq.to(torch.float32).contiguous()
+    if order is not None:
+        order = order.to(torch.int32).contiguous()
+    n_vert, P = prop.shape
+    K = idx.shape[1]
+    if (cat.dtype != torch.float32 or cat.dim() != 2 or cat.shape[0] != n_vert or cat.shape[1] != n_in + 2 * P
+            or not cat.is_contiguous()):
+        raise ValueError("gravnet_aggregate_into: cat must be a contiguous float32 [N, n_in + 2P] matrix")
+    argmax = torch.empty((n_vert, P), dtype=torch.int32, device=prop.device)
+    with torch.cuda.device(prop.device):
+        _cabi.check(_cabi.lib.fgc_gravnet_aggregate_fwd_ld(
+            _cabi.ptr(prop), _cabi.ptr(idx), _cabi.ptr(distsq), n_vert, K, P, _cabi.ptr(cat[:, n_in:n_in + P]),
+            _cabi.ptr(cat[:, n_in + P:]), n_in + 2 * P, _cabi.ptr(argmax), _cabi.ptr(order),
+            _cabi.current_stream(prop.device)), "fgc_gravnet_aggregate_fwd_ld")
+    return argmax
+
+
 @torch.library.custom_op("fgc_b200::gravnet_aggregate_cat", mutates_args=())
 def gravnet_aggregate_cat(x: Tensor, prop: Tensor, idx: Tensor, distsq: Tensor,
                           order: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
@@ -303,30 +327,46 @@ def _project_fused_ok(x: Tensor, w_space: Tensor, w_prop: Tensor) -> bool:
 
 
 def gravnet_project_eager(x: Tensor, w_space: Tensor, b_space: Optional[Tensor], w_prop: Tensor,
-                          b_prop: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+                          b_prop: Optional[Tensor], cat_extra: int = 0):
     """(space, propagate) = (x @ w_space^T + b_space, x @ w_prop^T + b_prop) in one pass over x; shapes
-    the fused kernel does not take go to the library GEMMs."""
+    the fused kernel does not take go to the library GEMMs.
+
+    cat_extra > 0: also returns a [N, C + cat_extra] matrix whose first C columns hold x (written by
+    the same pass; the other columns are left for the aggregation to fill)."""
+    n, C = x.shape
+    cat = None
+    if cat_extra > 0:
+        cat = torch.empty((n, C + cat_extra), dtype=torch.float32, device=x.device)
     if not _project_fused_ok(x, w_space, w_prop):
+        if cat is not None:
+            cat[:, :C].copy_(x)
+            return (torch.nn.functional.linear(x, w_space, b_space), torch.nn.functional.linear(x, w_prop, b_prop),
+                    cat)
         return (torch.nn.functional.linear(x, w_space, b_space), torch.nn.functional.linear(x, w_prop, b_prop))
     x = x.contiguous()
     w_space = w_space.contiguous()
     w_prop = w_prop.contiguous()
-    n, C = x.shape
     S, P = w_space.shape[0], w_prop.shape[0]
     space = torch.empty((n, S), dtype=torch.float32, device=x.device)
     prop = torch.empty((n, P), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _cabi.check(_cabi.lib.fgc_gravnet_project_fwd(
+        _cabi.check(_cabi.lib.fgc_gravnet_project_fwd_cat(
             _cabi.ptr(x), n, C, S, P, _cabi.ptr(w_space), _cabi.ptr(None if b_space is None else b_space.contiguous()),
             _cabi.ptr(w_prop), _cabi.ptr(None if b_prop is None else b_prop.contiguous()), _cabi.ptr(space),
-            _cabi.ptr(prop), _cabi.current_stream(x.device)), "fgc_gravnet_project_fwd")
+            _cabi.ptr(prop), _cabi.ptr(cat), C + cat_extra, _cabi.current_stream(x.device)),
+            "fgc_gravnet_project_fwd_cat")
+    if cat is not None:
+        return space, prop, cat
     return space, prop
 
 
 def gravnet_project_backward_eager(x: Tensor, w_space: Tensor, w_prop: Tensor, d_space: Optional[Tensor],
-                                   d_prop: Optional[Tensor], need_dx: bool
+                                   d_prop: Optional[Tensor], need_dx: bool, d_cat: Optional[Tensor] = None
                                    ) -> Tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
-    """(dx, dw_space, db_space, dw_prop, db_prop); dx is an empty tensor when need_dx is false."""
+    """(dx, dw_space, db_space, dw_prop, db_prop); dx is an empty tensor when need_dx is false.
+
+    d_cat (optional, [N, >= C], row-major): its first C columns are a second gradient of x and are
+    added to dx by the kernel that writes it."""
     n, C = x.shape
     S, P = w_space.shape[0], w_prop.shape[0]
     # (the fused kernel adds the CTAs' shares of the weight gradients with float atomics: with the
@@ -335,20 +375,29 @@ def gravnet_project_backward_eager(x: Tensor, w_space: Tensor, w_prop: Tensor, d
         ds = d_space if d_space is not None else x.new_zeros((n, S))
         dp = d_prop if d_prop is not None else x.new_zeros((n, P))
         dx = ds @ w_space + dp @ w_prop if need_dx else x.new_empty((0,))
+        if need_dx and d_cat is not None:
+            dx = dx + d_cat[:, :C]
         return dx, ds.t() @ x, ds.sum(0), dp.t() @ x, dp.sum(0)
     x = x.contiguous()
     ds = None if d_space is None else d_space.to(torch.float32).contiguous()
     dp = None if d_prop is None else d_prop.to(torch.float32).contiguous()
+    if d_cat is not None and need_dx:
+        d_cat = d_cat.to(torch.float32)
+        if d_cat.stride(1) != 1:
+            d_cat = d_cat.contiguous()
+    else:
+        d_cat = None
     dx = torch.empty_like(x) if need_dx else x.new_empty((0,))
     dws = torch.empty_like(w_space, memory_format=torch.contiguous_format)
     dwp = torch.empty_like(w_prop, memory_format=torch.contiguous_format)
     dbs = torch.empty((S,), dtype=torch.float32, device=x.device)
     dbp = torch.empty((P,), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
-        _cabi.check(_cabi.lib.fgc_gravnet_project_bwd(
+        _cabi.check(_cabi.lib.fgc_gravnet_project_bwd_cat(
             _cabi.ptr(x), n, C, S, P, _cabi.ptr(w_space.contiguous()), _cabi.ptr(w_prop.contiguous()), _cabi.ptr(ds),
-            _cabi.ptr(dp), _cabi.ptr(dx) if need_dx else None, _cabi.ptr(dws), _cabi.ptr(dbs), _cabi.ptr(dwp),
-            _cabi.ptr(dbp), _cabi.current_stream(x.device)), "fgc_gravnet_project_bwd")
+            _cabi.ptr(dp), _cabi.ptr(d_cat), 0 if d_cat is None else d_cat.stride(0),
+            _cabi.ptr(dx) if need_dx else None, _cabi.ptr(dws), _cabi.ptr(dbs), _cabi.ptr(dwp),
+            _cabi.ptr(dbp), _cabi.current_stream(x.device)), "fgc_gravnet_project_bwd_cat")
     return dx, dws, dbs, dwp, dbp
 
 

@@ -465,6 +465,25 @@ int fgc_gravnet_project_bwd(const float *x, int64_t n_rows, int32_t n_in, int32_
                             fgc_stream_t stream);
 
 /*
+ * The two projection calls for a layer that keeps [x | mean | max] as one matrix (gnn_ops.py:106):
+ * the forward also writes the rows of x into the first n_in columns of x_copy (row stride ld_copy
+ * floats; NULL: no copy), so the concatenation costs no pass of its own; the backward adds the
+ * first n_in columns of dx_add (row stride ld_add; the x columns of that matrix's gradient) to
+ * dx while it writes it, so the two gradients of x meet without an addition pass.
+ */
+int fgc_gravnet_project_fwd_cat(const float *x, int64_t n_rows, int32_t n_in, int32_t n_space,
+                                int32_t n_prop, const float *w_space, const float *b_space_or_null,
+                                const float *w_prop, const float *b_prop_or_null, float *out_space,
+                                float *out_prop, float *x_copy_or_null, int64_t ld_copy,
+                                fgc_stream_t stream);
+int fgc_gravnet_project_bwd_cat(const float *x, int64_t n_rows, int32_t n_in, int32_t n_space,
+                                int32_t n_prop, const float *w_space, const float *w_prop,
+                                const float *d_space_or_null, const float *d_prop_or_null,
+                                const float *dx_add_or_null, int64_t ld_add, float *dx_or_null,
+                                float *dw_space, float *db_space_or_null, float *dw_prop,
+                                float *db_prop_or_null, fgc_stream_t stream);
+
+/*
  * Conversions between row splits and PyTorch-Geometric style batch vectors on the device
  * (fastgraphcompute/torch_geometric_interface.py:4-42 row_splits_from_strict_batch and :45-74
  * strict_batch_from_row_splits of the reference, which use nonzero / repeat_interleave).

@@ -573,6 +573,44 @@ def test_gravnet_aggregate_into_concatenated_matrix():
     assert torch.equal(cat2, cat.detach())
 
 
+def test_gravnet_layer_front_matches_separate_calls():
+    """Projections + kNN + aggregation as the layer runs them in eager mode (x copied into
+    [x | mean | max] by the projection kernel, mean/max written in place, the two gradients of x added
+    inside the projection backward) against the same steps as separate calls with torch.cat: same
+    matrix bit for bit, gradients of x and of the four parameters within the tolerance of a
+    re-ordered fp32 sum.  Shapes: the benchmark layer, a width the fused projection does not take,
+    an input without gradient."""
+    from fastgraphcompute_b200.gnn_ops import gravnet_project, gravnet_project_and_aggregate
+    from fastgraphcompute_b200 import binned_select_knn
+    g = torch.Generator().manual_seed(77)
+    for n, C, S, P, K, x_grad in ((3000, 64, 4, 32, 12, True), (1500, 20, 3, 8, 9, True), (800, 64, 4, 32, 10, False)):
+        x = torch.randn((n, C), generator=g).to(DEV).requires_grad_(x_grad)
+        ws = (0.3 * torch.randn((S, C), generator=g)).to(DEV).requires_grad_(True)
+        bs = torch.randn((S,), generator=g).to(DEV).requires_grad_(True)
+        wp = (0.3 * torch.randn((P, C), generator=g)).to(DEV).requires_grad_(True)
+        bp = torch.randn((P,), generator=g).to(DEV).requires_grad_(True)
+        rs = torch.tensor([0, n // 3, n], dtype=torch.int64, device=DEV)
+        gc = torch.randn((n, C + 2 * P), generator=g).to(DEV)
+        gd = torch.randn((n, K), generator=g).to(DEV)
+        leaves = [t for t in (x, ws, bs, wp, bp) if t.requires_grad]
+
+        space, prop = gravnet_project(x, ws, bs, wp, bp)
+        idx, dsq = binned_select_knn(K, space, rs)
+        fmean, fmax = gravnet_aggregate(prop, idx, dsq)
+        ref = torch.cat([x, fmean, fmax], dim=1)
+        ((ref * gc).sum() + (dsq * gd).sum() + space.sum()).backward()
+        want = [t.grad.clone() for t in leaves]
+        for t in leaves:
+            t.grad = None
+
+        cat, idx2, dsq2, space2 = gravnet_project_and_aggregate(x, ws, bs, wp, bp, K, rs)
+        assert torch.equal(space2, space.detach()) and torch.equal(idx2, idx) and torch.equal(dsq2, dsq.detach())
+        assert torch.equal(cat, ref.detach())
+        ((cat * gc).sum() + (dsq2 * gd).sum() + space2.sum()).backward()
+        for t, w in zip(leaves, want):
+            parity.assert_grad_close(t.grad.cpu().numpy(), w.cpu().numpy(), 2e-5, "fused layer front")
+
+
 def test_gravnet_input_projections_vs_library_gemms():
     """The fused input projections (one pass over x forward, one backward) against the two
     torch.nn.functional.linear calls and their autograd, for the benchmark shape, odd shapes, the
