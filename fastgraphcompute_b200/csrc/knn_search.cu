@@ -38,6 +38,9 @@ struct KnnArgs {
     const uint8_t *sflag;   // nullptr: no direction restriction
     const int *bounds;      // cell boundaries, total_bins + 1 entries
     int *hardlist;          // queries handed over to k_knn_hard (cell-order positions)
+    float *hard_parts;      // k_knn_hard: partial lists of queries that several CTAs share
+    size_t hard_parts_bytes;
+    int *hard_tickets;      // k_knn_hard: finished parts per listed query (zero at launch)
     KnnGrid *grid;
     int64_t *out_idx;
     float *out_dist;
@@ -618,10 +621,16 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
     }
 }
 
-// The queries that gave up their walk in a large row split: one CTA per query, every warp scans
-// an interleaved eighth of the row split with a list of its own, warp 0 then offers the other
-// warps' lists to its own and writes the row.  Same candidates, same strict "<" rule, fixed
-// order: the result does not depend on which CTA picks the query up.
+// The queries that gave up their walk in a large row split: a whole CTA per query, every warp
+// scans an interleaved eighth of the candidates with a list of its own, warp 0 then offers the other
+// warps' lists to its own.  There are usually a handful of such queries and each scans up to
+// hundreds of thousands of points, so while the launch has more CTAs than queries a query is split
+// over S CTAs (a contiguous S-th of the row split each): every CTA stores its merged list, the one
+// that finishes last (ticket counter, no waiting) offers the S stored lists to a fresh list in part
+// order and writes the row.  Same candidates, same strict "<" rule, fixed orders: the result does
+// not depend on which CTA picks up what or finishes last.
+constexpr int kHardMaxSplit = 32;
+
 template <int NV, int R>
 __global__ void __launch_bounds__(kKnnWarps * 32)
 k_knn_hard(const KnnArgs a)
@@ -633,9 +642,23 @@ k_knn_hard(const KnnArgs a)
     KnnGrid *__restrict__ g = a.grid;
     if (g->status != 0) return;
     const int n_hard = min(g->n_hard, a.n_vert);
+    if (n_hard == 0) return;
     const int K = a.K, kn = K - 1, nc = a.n_coords;
     const uint8_t *__restrict__ sflag = a.sflag;
-    for (int h = blockIdx.x; h < n_hard; h += gridDim.x) {
+    // CTAs per query: what the launch has to spare, what the scratch for the stored lists holds
+    constexpr size_t kPartBytes = (size_t)R * 32 * 8;
+    long long S = (long long)gridDim.x / n_hard;
+    if (S > kHardMaxSplit) S = kHardMaxSplit;
+    const long long cap = (long long)(a.hard_parts_bytes / kPartBytes) / n_hard;
+    if (S > cap) S = cap;
+    if (S < 1 || n_hard > 1024 || !a.hard_parts || !a.hard_tickets) S = 1;     // (1024 tickets are cleared per search)
+    const int split = (int)S;
+    const long long units = (long long)n_hard * split;
+    float *__restrict__ part_d = a.hard_parts;
+    int *__restrict__ part_i = (int *)(a.hard_parts + (size_t)units * R * 32);
+
+    for (long long u = blockIdx.x; u < units; u += gridDim.x) {
+        const int h = (int)(u / split), part = (int)(u - (long long)h * split);
         const int qi = a.hardlist[h];
         float4 q[NV];
 #pragma unroll
@@ -644,6 +667,9 @@ k_knn_hard(const KnnArgs a)
         const int e = __ldg(a.sbin + qi) / B;
         const int ev_begin = __ldg(a.bounds + e * B);
         const int n_e = __ldg(a.bounds + (e + 1) * B) - ev_begin;
+        // this CTA's share of the row split
+        const int chunk = (int)(((long long)n_e + split - 1) / split);
+        const int t_lo = part * chunk, t_hi = min(n_e, t_lo + chunk);
         NeighbourList<R> list;
         list.init(lane, kn);
         auto offer_all = [&](float dc, int j) {
@@ -654,10 +680,10 @@ k_knn_hard(const KnnArgs a)
                 list.offer(lane, __shfl_sync(FGC_FULL_MASK, dc, src), __shfl_sync(FGC_FULL_MASK, j, src));
             }
         };
-        for (int t = wib * 32; t < n_e; t += kKnnWarps * 32) {
+        for (int t = t_lo + wib * 32; t < t_hi; t += kKnnWarps * 32) {
             const int j = ev_begin + t + lane;
             float dc = __uint_as_float(kInfBits);
-            if (t + lane < n_e) {
+            if (t + lane < t_hi) {
                 float4 c[NV];
 #pragma unroll
                 for (int v = 0; v < NV; v++) c[v] = __ldg(a.scoords + (size_t)j * NV + v);
@@ -673,6 +699,7 @@ k_knn_hard(const KnnArgs a)
             s_i[wib][r * 32 + lane] = list.id[r];
         }
         __syncthreads();
+        bool write_row = false;
         if (wib == 0) {
             for (int w = 1; w < kKnnWarps; w++)
 #pragma unroll
@@ -682,18 +709,47 @@ k_knn_hard(const KnnArgs a)
                     const float dc = j >= 0 ? s_d[w][r * 32 + lane] : __uint_as_float(kInfBits);
                     offer_all(dc, j);
                 }
-            const int orig_q = __ldg(a.sorig + qi);
-            int64_t *__restrict__ out_i = a.out_idx + (size_t)orig_q * K;
-            float *__restrict__ out_d = a.out_dist + (size_t)orig_q * K;
-            if (lane == 0) { out_i[0] = orig_q; out_d[0] = 0.f; }
-            const int64_t pad = a.tf_compat ? (int64_t)orig_q : (int64_t)-1;
+            write_row = split == 1;
+            if (split > 1) {
+                // store this part's list, then see whether it was the last one
 #pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int s = lane * R + r;
-                if (s < kn) {
-                    const bool filled = __float_as_uint(list.d[r]) < kInfBits && list.id[r] >= 0;
-                    out_i[1 + s] = filled ? (int64_t)__ldg(a.sorig + list.id[r]) : pad;
-                    out_d[1 + s] = filled ? list.d[r] : 0.f;
+                for (int r = 0; r < R; r++) {
+                    part_d[(size_t)u * R * 32 + r * 32 + lane] = list.d[r];
+                    part_i[(size_t)u * R * 32 + r * 32 + lane] = list.id[r];
+                }
+                __threadfence();
+                __syncwarp();
+                int ticket = 0;
+                if (lane == 0) ticket = atomicAdd(&a.hard_tickets[h], 1);
+                ticket = __shfl_sync(FGC_FULL_MASK, ticket, 0);
+                if (ticket == split - 1) {
+                    __threadfence();
+                    list.init(lane, kn);
+                    for (int p = 0; p < split; p++)
+#pragma unroll
+                        for (int r = 0; r < R; r++) {
+                            const size_t at = ((size_t)h * split + p) * R * 32 + r * 32 + lane;
+                            const int j = __ldcg(part_i + at);
+                            const float dc = j >= 0 ? __ldcg(part_d + at) : __uint_as_float(kInfBits);
+                            offer_all(dc, j);
+                        }
+                    write_row = true;
+                }
+            }
+            if (write_row) {
+                const int orig_q = __ldg(a.sorig + qi);
+                int64_t *__restrict__ out_i = a.out_idx + (size_t)orig_q * K;
+                float *__restrict__ out_d = a.out_dist + (size_t)orig_q * K;
+                if (lane == 0) { out_i[0] = orig_q; out_d[0] = 0.f; }
+                const int64_t pad = a.tf_compat ? (int64_t)orig_q : (int64_t)-1;
+#pragma unroll
+                for (int r = 0; r < R; r++) {
+                    const int s = lane * R + r;
+                    if (s < kn) {
+                        const bool filled = __float_as_uint(list.d[r]) < kInfBits && list.id[r] >= 0;
+                        out_i[1 + s] = filled ? (int64_t)__ldg(a.sorig + list.id[r]) : pad;
+                        out_d[1 + s] = filled ? list.d[r] : 0.f;
+                    }
                 }
             }
         }
@@ -765,6 +821,9 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     a.sflag = has_direction ? (const uint8_t *)(ws + L.sflag) : nullptr;
     a.bounds = (const int *)(ws + L.counts);
     a.hardlist = (int *)(ws + L.stmp);        // free since the grid build
+    a.hard_parts = (float *)(ws + L.pbin);    // (so are pbin and prank)
+    a.hard_parts_bytes = sizeof(int32_t) * (size_t)n_vert;
+    a.hard_tickets = (int *)(ws + L.prank);
     a.grid = (KnnGrid *)(ws + L.header);
     a.out_idx = out_idx;
     a.out_dist = out_distsq;
@@ -777,6 +836,8 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     // than once (the build/search split), and a count left by an earlier search would make
     // this one re-scan stale entries and append behind them.
     FGC_RETURN_IF_CUDA(cudaMemsetAsync(&a.grid->n_hard, 0, sizeof(int32_t), s));
+    // (one ticket per listed query that is split over several CTAs: fewer than the CTAs of the launch)
+    FGC_RETURN_IF_CUDA(cudaMemsetAsync(a.hard_tickets, 0, sizeof(int32_t) * (size_t)(n_vert < 1024 ? n_vert : 1024), s));
     if (n_coords <= 3) return launch_knn_nv<1, 0>(a, s);
     if (L.nv == 1) {
         // D = 4: a caller that fixed the grid's form at build time says so here too and gets the

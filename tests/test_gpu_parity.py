@@ -341,17 +341,20 @@ def test_knn_and_backward_stay_inside_their_output_buffers():
         parity.assert_knn_parity(idx.cpu().numpy(), dsq.cpu().numpy(), oidx, odsq, what="canary case")
 
 
-@pytest.mark.parametrize("K", [20, 100])
-def test_knn_repeated_search_on_one_grid(K):
+@pytest.mark.parametrize("K,n_out", [(20, 60), (40, 5), (100, 60), (20, 400)])
+def test_knn_repeated_search_on_one_grid(K, n_out):
     """The build/search split: one grid, searched three times.  Clustered points with far
     outliers in a row split of more than 4096 points make some walks give up, so every search
     fills the list of queries for k_knn_hard; the list must start empty each time (same rows,
-    same list length, the workspace's cell order untouched) -- and the rows must be right."""
+    same list length, the workspace's cell order untouched) -- and the rows must be right.
+    The number of outliers decides over how many CTAs k_knn_hard splits one query (5: as many as
+    it allows, 60: a few, 400: one CTA per query); K picks the list's form (one, two, four slots
+    per lane)."""
     from fastgraphcompute_b200 import _cabi
     import importlib
     km = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
     g = torch.Generator().manual_seed(17)
-    n_in, n_out = 12000, 60
+    n_in = 12000
     pts = torch.cat([0.5 + 0.002 * torch.randn((n_in, 3), generator=g),
                      200.0 * torch.rand((n_out, 3), generator=g) - 100.0])
     pts = pts[torch.randperm(pts.shape[0], generator=g)].contiguous()
