@@ -180,6 +180,7 @@ class EventRowExchange:
                      for dtype, shape, device in templates]
         self.pending = []
         self.keep = []
+        self.groups = []          # per post(): (works, row ranges of every rank's events, event after the own-row copies)
         self.comm_stream = None
         dev = templates[0][2]
         if torch.device(dev).type == "cuda":
@@ -223,16 +224,48 @@ class EventRowExchange:
                             ops.append(dist.P2POp(dist.irecv, full[self.rs[e]: self.rs[e] + sz],
                                                   self._global_rank(p), self.group))
         self.keep.append(blocks)
-        if not ops:
-            return
+        ranges = []
+        if self.receives:
+            for r in range(self.world):
+                for e in events_of_rank[r]:
+                    if self.rs[e + 1] > self.rs[e]:
+                        ranges.append((self.rs[e], self.rs[e + 1]))
+        copied = None
         if self.comm_stream is not None:
-            # issue from a side stream that waits for the producer of the blocks: the launching
-            # stream is free to start the next group's search while these transfers run
-            self.comm_stream.wait_stream(torch.cuda.current_stream(self.comm_stream.device))
-            with torch.cuda.stream(self.comm_stream):
-                self.pending.extend(dist.batch_isend_irecv(ops))
+            copied = torch.cuda.Event()
+            copied.record(torch.cuda.current_stream(self.comm_stream.device))
+        works = []
+        if ops:
+            if self.comm_stream is not None:
+                # issue from a side stream that waits for the producer of the blocks: the launching
+                # stream is free to start the next group's search while these transfers run
+                self.comm_stream.wait_stream(torch.cuda.current_stream(self.comm_stream.device))
+                with torch.cuda.stream(self.comm_stream):
+                    works = dist.batch_isend_irecv(ops)
+            else:
+                works = dist.batch_isend_irecv(ops)
+        self.pending.extend(works)
+        self.groups.append((works, ranges, copied))
+
+    def wait_group(self, i, stream=None):
+        """Make ``stream`` (CUDA; on CPU: the caller) wait until the rows of the i-th posted group
+        are in the full tensors -- the transfers and this rank's own copies -- and return their
+        row ranges [(begin, end), ...].  Lets a caller work on a finished group (widen its ids)
+        while later groups are still searched or in flight."""
+        works, ranges, copied = self.groups[i]
+        if stream is not None:
+            with torch.cuda.stream(stream):
+                for w in works:
+                    w.wait()
+            if copied is not None:
+                stream.wait_event(copied)
         else:
-            self.pending.extend(dist.batch_isend_irecv(ops))
+            for w in works:
+                w.wait()
+            # (host waits are final: finish() must not wait for these a second time)
+            done = set(id(w) for w in works)
+            self.pending = [w for w in self.pending if id(w) not in done]
+        return ranges
 
     def finish(self):
         """Wait for every posted transfer; returns the full tensors (None on a rank that does not
@@ -247,6 +280,7 @@ class EventRowExchange:
                 w.wait()
         self.pending = []
         self.keep = []
+        self.groups = []
         return self.full
 
 
@@ -303,7 +337,29 @@ def sharded_binned_select_knn(K, coords, row_splits, direction=None, torch_compa
     chunks = [chunk_events(part.events[r], row_splits, n_chunks) for r in range(world)]
     ex = EventRowExchange(row_splits, part, [(torch.int32, (K,), coords.device), (torch.float32, (K,), coords.device)],
                           mode, root, group)
-    for c in range(max(int(n_chunks), 1)):
+    # the public ids are int64: a finished group is widened on a stream of its own while the
+    # next group is searched and in flight
+    full_idx = None
+    widen_stream = None
+    if ex.receives:
+        full_idx = torch.empty((ex.rs[-1], K), dtype=torch.int64, device=coords.device)
+        if coords.is_cuda:
+            widen_stream = torch.cuda.Stream(device=coords.device)
+
+    def widen(i):
+        if full_idx is None:
+            return
+        ranges = ex.wait_group(i, widen_stream)
+        if widen_stream is not None:
+            with torch.cuda.stream(widen_stream):
+                for a, b in ranges:
+                    full_idx[a:b].copy_(ex.full[0][a:b], non_blocking=True)
+        else:
+            for a, b in ranges:
+                full_idx[a:b].copy_(ex.full[0][a:b])
+
+    n_groups = max(int(n_chunks), 1)
+    for c in range(n_groups):
         mine = chunks[rank][c]
         if mine:
             rows, idx, dsq = local_binned_select_knn(K, coords, row_splits, mine, direction,
@@ -313,10 +369,16 @@ def sharded_binned_select_knn(K, coords, row_splits, direction=None, torch_compa
             blocks = [torch.empty((0, K), dtype=torch.int32, device=coords.device),
                       torch.empty((0, K), dtype=torch.float32, device=coords.device)]
         ex.post(mine, blocks, [chunks[r][c] for r in range(world)])
+        if c > 0:
+            widen(c - 1)
+    widen(n_groups - 1)
     full_idx32, full_dsq = ex.finish()
     if full_idx32 is None:
         return None, None
-    return full_idx32.to(torch.int64), full_dsq
+    if widen_stream is not None:
+        torch.cuda.current_stream(coords.device).wait_stream(widen_stream)
+        full_idx32.record_stream(widen_stream)
+    return full_idx, full_dsq
 
 
 def allreduce_gradients(parameters, group=None):
