@@ -8,8 +8,8 @@
 // One warp per row: the lanes take the K slots (coalesced idx / grad loads), the
 // row's own term is reduced inside the warp and leaves as ONE add per
 // coordinate, the neighbour term leaves as one reduction per slot: a 16-byte
-// (D = 4) or 8-byte (D = 2) vector reduction, else one fp32 reduction per
-// coordinate.  (Summing the neighbour terms of 64 cell-adjacent rows per target in a
+// (D = 4; two of them for D = 8) or 8-byte (D = 2) vector reduction, else one fp32
+// reduction per coordinate.  (Summing the neighbour terms of 64 cell-adjacent rows per target in a
 // shared-memory hash table first, one reduction per distinct target and CTA, was measured
 // at twice the time: float adds on shared memory plus the probe cost more than the L2
 // reductions they save; without any reductions the kernel would be 22 % faster.)
@@ -49,11 +49,15 @@ k_knn_bwd(const float *__restrict__ grad_distsq, const int64_t *__restrict__ idx
                 if (n >= 0 && n < n_vert) {
                     const float g2 = 2.f * grad_distsq[(size_t)i * K + k];
                     float c[DM], xn[DM];
-                    if (D == 4 && vec_ok) {
-                        // one 16-byte gather instead of four 4-byte ones: the kernel is bound by
-                        // L1TEX requests (C2: 0.099 -> 0.080 ms)
-                        const float4 t4 = __ldg((const float4 *)coords + n);
-                        xn[0] = t4.x; xn[1 % DM] = t4.y; xn[2 % DM] = t4.z; xn[3 % DM] = t4.w;
+                    if ((D == 4 || D == 8) && vec_ok) {
+                        // 16-byte gathers instead of 4-byte ones: the kernel is bound by L1TEX
+                        // requests (C2: 0.099 -> 0.080 ms)
+#pragma unroll
+                        for (int q4 = 0; q4 < DM / 4; q4++) {
+                            const float4 t4 = __ldg((const float4 *)(coords + (size_t)n * DM) + q4);
+                            xn[(4 * q4) % DM] = t4.x; xn[(4 * q4 + 1) % DM] = t4.y;
+                            xn[(4 * q4 + 2) % DM] = t4.z; xn[(4 * q4 + 3) % DM] = t4.w;
+                        }
                     } else {
 #pragma unroll
                         for (int v = 0; v < DM; v++) xn[v] = __ldg(coords + (size_t)n * nc + v);
@@ -64,8 +68,13 @@ k_knn_bwd(const float *__restrict__ grad_distsq, const int64_t *__restrict__ idx
                         self[v] -= c[v];
                     }
                     // one vector reduction per neighbour where the row is 8 or 16 bytes wide
-                    if (D == 4 && vec_ok)
-                        atomicAdd((float4 *)(out + (size_t)n * 4), make_float4(c[0], c[1 % DM], c[2 % DM], c[3 % DM]));
+                    if ((D == 4 || D == 8) && vec_ok) {
+#pragma unroll
+                        for (int q4 = 0; q4 < DM / 4; q4++)
+                            atomicAdd((float4 *)(out + (size_t)n * DM) + q4,
+                                      make_float4(c[(4 * q4) % DM], c[(4 * q4 + 1) % DM], c[(4 * q4 + 2) % DM],
+                                                  c[(4 * q4 + 3) % DM]));
+                    }
                     else if (D == 2 && vec_ok)
                         atomicAdd((float2 *)(out + (size_t)n * 2), make_float2(c[0], c[1 % DM]));
                     else {
@@ -134,6 +143,7 @@ extern "C" int fgc_binned_knn_bwd_ordered(const float *grad_distsq, const int64_
     case 2: k_knn_bwd<2><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
     case 3: k_knn_bwd<3><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
     case 4: k_knn_bwd<4><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
+    case 8: k_knn_bwd<8><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
     default: k_knn_bwd<0><<<blocks, T, 0, s>>>(grad_distsq, idx, coords, n, K, n_coords, out_grad_coords, vec_ok, order_or_null); break;
     }
     FGC_CHECK_LAUNCH();

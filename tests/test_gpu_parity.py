@@ -441,6 +441,36 @@ def test_knn_gradient_reference_style():
         assert torch.allclose(g.double(), gb, atol=1e-5, rtol=1e-3)
 
 
+@pytest.mark.parametrize("D", [3, 6, 8])
+def test_knn_backward_padded_path_matches_direct_kernel(D):
+    """At size the backward for D = 3 (5, 6, 7) runs the four- (eight-) coordinate kernel on a
+    zero-padded copy: same gradient as the kernel for that D (float sums in another order) and as
+    the oracle.  D = 8 takes the two-vector kernel directly."""
+    import importlib
+    km = importlib.import_module("fastgraphcompute_b200.extensions.binned_select_knn")
+    g = torch.Generator().manual_seed(23)
+    n, K = 70000, 32
+    assert n * K >= km.pad_min_pairs
+    pts = torch.rand((n, D), generator=g)
+    rs = torch.tensor([0, 30000, n], dtype=torch.int64)
+    grad = torch.randn((n, K), generator=g)
+    got = []
+    for limit in (km.pad_min_pairs, 1 << 60):
+        old = km.pad_min_pairs
+        km.pad_min_pairs = limit
+        try:
+            c = pts.to(DEV).requires_grad_(True)
+            idx, dsq = fgc.binned_select_knn(K, c, rs.to(DEV))
+            (dsq * grad.to(DEV)).sum().backward()
+            got.append((idx.cpu().numpy(), c.grad.cpu().numpy()))
+        finally:
+            km.pad_min_pairs = old
+    assert got[0][1].shape == (n, D)
+    parity.assert_grad_close(got[0][1], got[1][1], 1e-5, "padded against direct")
+    og = oracle.binned_select_knn_grad(grad.numpy(), got[0][0], pts.numpy())
+    parity.assert_grad_close(got[0][1], og, 1e-5, "padded against the oracle")
+
+
 def test_knn_edge_cases_and_errors():
     c = torch.rand((50, 3), device=DEV)
     rs = torch.tensor([0, 50], device=DEV)
