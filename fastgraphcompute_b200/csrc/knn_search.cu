@@ -328,10 +328,10 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
     // Sorted list where it was measured faster than the unordered one (B200, uniform, normal and
     // clustered data in 3 to 8 dimensions, K = 8..64): one slot per lane (-2 to -20 %, except
     // uniform 3-D data at K = 32, +7 %: few insertions follow the first sort there), two slots
-    // per lane with one float4 per point (-10 to -23 % for K = 40, 48; -1 to -15 % for K = 64).
-    // Two slots with more than four coordinates lose 3 to 4 % (registers), four and more slots
-    // per lane keep the unordered list.
-    constexpr bool SORTED = R == 1 || (R == 2 && NV == 1);
+    // per lane (-10 to -23 % for K = 40, 48 and -1 to -15 % for K = 64 with one float4 per point;
+    // -2 to -5 % with more than four coordinates, where it needs the registers of 6 instead of 7
+    // resident CTAs).  Four and more slots per lane keep the unordered list.
+    constexpr bool SORTED = R <= 2;
     typename std::conditional<SORTED, SortedList<R>, NeighbourList<R>>::type list;
     list.init(lane, kn);
     unsigned cnt_evals = 0, cnt_steps = 0, cnt_ins = 0, cnt_batches = 0, cnt_shells = 0, cnt_brute = 0;
@@ -761,7 +761,7 @@ k_knn_hard(const KnnArgs a)
 // build decides on the device between the two -- one launch, one uniform branch (two launches
 // of which one returns at once cost the same; out-of-line bodies were slower).
 template <int NV, int R, bool COUNT, int MODE>
-__global__ void __launch_bounds__(kKnnWarps * 32, (R == 1 ? 8 : (R == 2 ? 7 : (R == 4 ? 6 : 4))))
+__global__ void __launch_bounds__(kKnnWarps * 32, (R == 1 ? 8 : (R == 2 ? (NV == 1 ? 7 : 6) : (R == 4 ? 6 : 4))))
 k_knn(const KnnArgs a)
 {
     if (MODE == 0) knn_query<NV, R, COUNT, false>(a);
