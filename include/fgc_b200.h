@@ -159,6 +159,8 @@ int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,
  * whether the grid was built with a direction array.  flags: FGC_SEARCH_COUNT accumulates
  * the debug counters in the workspace (fgc_knn_read_counters).  A built grid may be searched
  * any number of times (other K is not allowed: the workspace layout depends on the arguments).
+ * Two searches of one workspace must not overlap in time (they share the list of queries that
+ * gave up their walk and its scratch, which a search clears when it starts).
  *
  * When the status word of the workspace is non-zero after the grid build (non-finite
  * coordinate, malformed row_splits; see fgc_read_status) no neighbour is searched: every row
