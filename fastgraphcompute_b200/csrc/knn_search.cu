@@ -67,20 +67,36 @@ constexpr int kHardMin = 4096;
 
 // Squared distance over NV float4 chunks.  Order and rounding: acc = acc + (a-b)*(a-b)
 // per dimension, dimension 0 first, no fused multiply-add; the first term needs no add.
+// The coordinates beyond n_coords are stored as 0 on both sides, so their terms are +0 and adding
+// them changes no bit: all 4 NV components are computed, the differences and squares two at a
+// time with the packed fp32x2 instructions of sm_100 (same rounding as the scalar ones).
+__device__ __forceinline__ unsigned long long pack_f32x2(float a, float b)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void sq_diff_f32x2(float a0, float a1, float b0, float b1, float &s0, float &s1)
+{
+    unsigned long long d, s;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(pack_f32x2(a0, a1)), "l"(pack_f32x2(b0, b1)));
+    asm("mul.rn.f32x2 %0, %1, %1;" : "=l"(s) : "l"(d));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(s));
+}
 template <int NV>
 __device__ __forceinline__ float dist_sq(const float4 (&q)[NV], const float4 (&c)[NV], int n_coords)
 {
-    float d = __fsub_rn(q[0].x, c[0].x);
-    float acc = __fmul_rn(d, d);
-    d = __fsub_rn(q[0].y, c[0].y); acc = __fadd_rn(acc, __fmul_rn(d, d));   // n_coords >= 2
-    if (2 < n_coords) { d = __fsub_rn(q[0].z, c[0].z); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
-    if (3 < n_coords) { d = __fsub_rn(q[0].w, c[0].w); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
+    (void)n_coords;
+    float acc = 0.f;
 #pragma unroll
-    for (int v = 1; v < NV; v++) {
-        if (4 * v + 0 < n_coords) { d = __fsub_rn(q[v].x, c[v].x); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
-        if (4 * v + 1 < n_coords) { d = __fsub_rn(q[v].y, c[v].y); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
-        if (4 * v + 2 < n_coords) { d = __fsub_rn(q[v].z, c[v].z); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
-        if (4 * v + 3 < n_coords) { d = __fsub_rn(q[v].w, c[v].w); acc = __fadd_rn(acc, __fmul_rn(d, d)); }
+    for (int v = 0; v < NV; v++) {
+        float s0, s1, s2, s3;
+        sq_diff_f32x2(q[v].x, q[v].y, c[v].x, c[v].y, s0, s1);
+        sq_diff_f32x2(q[v].z, q[v].w, c[v].z, c[v].w, s2, s3);
+        acc = v == 0 ? s0 : __fadd_rn(acc, s0);
+        acc = __fadd_rn(acc, s1);
+        acc = __fadd_rn(acc, s2);
+        acc = __fadd_rn(acc, s3);
     }
     return acc;
 }
