@@ -70,12 +70,6 @@ constexpr int kHardMin = 4096;
 // The coordinates beyond n_coords are stored as 0 on both sides, so their terms are +0 and adding
 // them changes no bit: all 4 NV components are computed, the differences and squares two at a
 // time with the packed fp32x2 instructions of sm_100 (same rounding as the scalar ones).
-__device__ __forceinline__ unsigned long long pack_f32x2(float a, float b)
-{
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
 __device__ __forceinline__ void sq_diff_f32x2(float a0, float a1, float b0, float b1, float &s0, float &s1)
 {
     unsigned long long d, s;
