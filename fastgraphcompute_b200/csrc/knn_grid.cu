@@ -179,6 +179,7 @@ __device__ void grid_setup(KnnGrid *g, const int64_t *__restrict__ row_splits, i
     g->B = (int)B;
     g->n_events = n_events;
     g->total_bins = (int)(B * n_events);
+    grid_set_divisors(g);
     g->w = w;
     g->inv_w = __fdiv_rn(1.0f, w);
     g->slack = 4e-6f * fmaxf(ext_max, w);
@@ -237,6 +238,7 @@ __device__ void grid_refine(KnnGrid *g, unsigned long long sum_sq, int n_vert, f
         g->n[0] = n[0]; g->n[1] = n[1]; g->n[2] = n[2]; g->n[3] = 1;
         g->B = (int)B3;
         g->total_bins = (int)(B3 * g->n_events);
+        grid_set_divisors(g);
         g->w = w;
         g->inv_w = __fdiv_rn(1.0f, w);
         g->slack = 4e-6f * fmaxf(ext_max, w);
@@ -257,6 +259,7 @@ __device__ void grid_refine(KnnGrid *g, unsigned long long sum_sq, int n_vert, f
     g->n[0] = n[0]; g->n[1] = n[1]; g->n[2] = n[2]; g->n[3] = n[3];
     g->B = (int)B;
     g->total_bins = (int)(B * g->n_events);
+    grid_set_divisors(g);
     g->w = w;
     g->inv_w = __fdiv_rn(1.0f, w);
     g->slack = 4e-6f * fmaxf(ext_max, w);

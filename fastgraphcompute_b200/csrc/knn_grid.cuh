@@ -48,8 +48,33 @@ struct KnnGrid {
     // optional debug counters (filled when a search is launched with count_evals):
     // [0] distance evaluations, [1] 32-candidate steps, [2] list insertions,
     // [3] 32-item metadata batches, [4] shells, [5] queries that scanned their whole row split
-    unsigned long long counters[8];
+    unsigned long long counters[6];
+    // division of a cell id by B, n1*n2*n3, n2*n3 and n3 as multiply + shift (grid_set_divisors)
+    uint32_t div_m[4];
+    uint32_t div_s[4];
 };
+
+// x / d for 0 <= x < 2^31 and 1 <= d < 2^31 as (x * m) >> s with m = ceil(2^s / d),
+// s = 31 + ceil(log2 d): exact for every such x (m < 2^32, the product fits 64 bits).
+__host__ __device__ inline void fast_div_setup(uint32_t d, uint32_t &m, uint32_t &s)
+{
+    uint32_t l = 0;
+    while (l < 31 && (1u << l) < d) l++;
+    s = 31 + l;
+    m = (uint32_t)((((unsigned long long)1 << s) + d - 1) / d);
+}
+__device__ __forceinline__ int fast_div(int x, uint32_t m, uint32_t s)
+{
+    return (int)(((unsigned long long)(uint32_t)x * m) >> s);
+}
+__host__ __device__ inline void grid_set_divisors(KnnGrid *g)
+{
+    const uint32_t n1 = (uint32_t)g->n[1], n2 = (uint32_t)g->n[2], n3 = (uint32_t)g->n[3];
+    fast_div_setup((uint32_t)g->B, g->div_m[0], g->div_s[0]);
+    fast_div_setup(n1 * n2 * n3, g->div_m[1], g->div_s[1]);
+    fast_div_setup(n2 * n3, g->div_m[2], g->div_s[2]);
+    fast_div_setup(n3, g->div_m[3], g->div_s[3]);
+}
 
 // Items of the Chebyshev shell of radius d around a cell, in units of "line segments": a
 // segment is a run of consecutive cells along the last grid dimension, i.e. one contiguous

@@ -414,13 +414,14 @@ __device__ __forceinline__ void knn_query(const KnnArgs &a)
     if (!q_inactive && kn > 0) {
         const int B = g->B, n0 = g->n[0], n1 = g->n[1], n2 = g->n[2], n3 = G4 ? g->n[3] : 1;
         const int flat = __ldg(a.sbin + qi);
-        const int e = flat / B;
+        // (divisions by the grid's shape as multiply + shift: the divisors are set with the grid)
+        const int e = fast_div(flat, g->div_m[0], g->div_s[0]);
         int rem = flat - e * B;
-        const int b0 = rem / (n1 * n2 * n3);
+        const int b0 = fast_div(rem, g->div_m[1], g->div_s[1]);
         rem -= b0 * n1 * n2 * n3;
-        const int b1 = rem / (n2 * n3);
+        const int b1 = fast_div(rem, g->div_m[2], g->div_s[2]);
         rem -= b1 * n2 * n3;
-        const int b2 = G4 ? rem / n3 : rem;
+        const int b2 = G4 ? fast_div(rem, g->div_m[3], g->div_s[3]) : rem;
         const int b3 = G4 ? rem - b2 * n3 : 0;
         // the run of an item lies along the last grid dimension
         const int bl = G4 ? b3 : b2, nl = G4 ? n3 : n2;
