@@ -605,22 +605,22 @@ def run_b200(args):
             c3_coords = w3.coords.to(dev)
             c3_rs = w3.row_splits.to(dev)
 
-            def c3_run(mode, chunks):
+            def c3_run(mode, chunks, exchange="auto"):
                 if world == 1 or mode == "none":
                     return event_sharding.local_binned_select_knn(w3.K, c3_coords, w3.row_splits, part.events[rank])
                 return event_sharding.sharded_binned_select_knn(w3.K, c3_coords, w3.row_splits, gather=mode,
-                                                                n_chunks=chunks, check=False)
+                                                                n_chunks=chunks, check=False, exchange=exchange)
 
-            def c3_time(mode, chunks):
-                for _ in range(2):
-                    res = c3_run(mode, chunks)
+            def c3_time(mode, chunks, exchange="auto"):
+                for _ in range(3):        # (the first collective of a kind and size sets up its connections)
+                    res = c3_run(mode, chunks, exchange)
                 del res
                 barrier()
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
                 for _ in range(c3_reps):
-                    res = c3_run(mode, chunks)
+                    res = c3_run(mode, chunks, exchange)
                 e1.record()
                 torch.cuda.synchronize(dev)
                 del res
@@ -630,6 +630,7 @@ def run_b200(args):
             if world > 1:
                 c3_local["all"] = c3_time("all", 3)
                 c3_local["all_one_group"] = c3_time("all", 1)
+                c3_local["all_p2p"] = c3_time("all", 3, "p2p")
                 c3_local["root"] = c3_time("root", 3)
                 # correctness of the exchange, on every rank: same distances bit for bit and same
                 # neighbour sets as one GPU searching the whole batch
@@ -651,12 +652,14 @@ def run_b200(args):
             if world > 1:
                 c3["search_and_gather_all_ms"] = max_over_ranks(c3_local["all"])
                 c3["search_and_gather_all_one_group_ms"] = max_over_ranks(c3_local["all_one_group"])
+                c3["search_and_gather_all_point_to_point_ms"] = max_over_ranks(c3_local["all_p2p"])
                 c3["search_and_gather_root_ms"] = max_over_ranks(c3_local["root"])
                 c3["gathered_equals_single_gpu"] = all_ranks_ok(c3_local["equal"])
                 c3["gather_note"] = ("search + exchange of idx (int32 on the wire, widened to int64 on receipt) and "
-                                     "distsq, per-event point-to-point blocks (NCCL) into the final tensors; "
-                                     "'all': every rank ends with all rows, three groups of events per rank so that "
-                                     "transfers overlap the search; 'root': rank 0 only")
+                                     "distsq; 'all': every rank ends with all rows -- one NCCL all-gather per group "
+                                     "of events into a staging buffer, then a placing pass, three groups per rank so "
+                                     "that transfers overlap the search ('point_to_point': per-event blocks sent "
+                                     "straight into the final tensors instead); 'root': rank 0 only, point-to-point")
         c3_coords = None
 
     # ---- object-condensation index matrices (the loss-side consumer of the same row splits) --

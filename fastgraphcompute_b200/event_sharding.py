@@ -304,9 +304,88 @@ def gather_rows(rows, tensors, n_total, points_per_rank, group=None, row_splits=
     return ex.finish()
 
 
+def _gather_all_collective(K, coords, row_splits, chunks, search, group, rank, world):
+    """Rows of every rank on every rank through one all-gather per group of events.
+
+    The partition balances the ranks' row counts to a fraction of a per cent, so padding every
+    rank's block of a group to the largest one costs next to nothing, and an all-gather moves the
+    same bytes at the collective's bandwidth (NCCL rings / NVSwitch) where grouped point-to-point
+    transfers reached about half of it.  Every rank then has all blocks in shard order in a staging
+    buffer of its own memory; one pass per event places the rows at their global positions and
+    widens the ids to int64 (the pass the ids need anyway).  Group c is in flight while group c+1
+    is searched and group c-1 is placed."""
+    rs = [int(v) for v in torch.as_tensor(row_splits).cpu().tolist()]
+    n_total = rs[-1]
+    dev = coords.device
+    cuda = dev.type == "cuda"
+    full_idx = torch.empty((n_total, K), dtype=torch.int64, device=dev)
+    full_dsq = torch.empty((n_total, K), dtype=torch.float32, device=dev)
+    comm_stream = torch.cuda.Stream(device=dev) if cuda else None
+    place_stream = torch.cuda.Stream(device=dev) if cuda else None
+    groups = []
+
+    def place(g):
+        works, staged_i, staged_d, m, c = g[:5]
+        ctx = torch.cuda.stream(place_stream) if cuda else None
+        if ctx is not None:
+            ctx.__enter__()
+        try:
+            for w in works:
+                w.wait()
+            for r in range(world):
+                off = r * m
+                for e in chunks[r][c]:
+                    sz = rs[e + 1] - rs[e]
+                    if sz:
+                        full_idx[rs[e]: rs[e] + sz].copy_(staged_i[off: off + sz], non_blocking=True)
+                        full_dsq[rs[e]: rs[e] + sz].copy_(staged_d[off: off + sz], non_blocking=True)
+                    off += sz
+        finally:
+            if ctx is not None:
+                ctx.__exit__(None, None, None)
+
+    n_groups = len(chunks[rank])
+    for c in range(n_groups):
+        rows_of = [sum(rs[e + 1] - rs[e] for e in chunks[r][c]) for r in range(world)]
+        m = max(rows_of)
+        if m == 0:
+            groups.append(None)
+            continue
+        send_i = torch.empty((m, K), dtype=torch.int32, device=dev)
+        send_d = torch.empty((m, K), dtype=torch.float32, device=dev)
+        mine = chunks[rank][c]
+        if mine:
+            _, idx, dsq = search(mine)
+            if idx.shape[0] != rows_of[rank]:
+                raise RuntimeError("shard of rank %d has %d rows, the partition table says %d"
+                                   % (rank, idx.shape[0], rows_of[rank]))
+            send_i[: idx.shape[0]].copy_(idx)
+            send_d[: idx.shape[0]].copy_(dsq)
+        staged_i = torch.empty((world * m, K), dtype=torch.int32, device=dev)
+        staged_d = torch.empty((world * m, K), dtype=torch.float32, device=dev)
+        if cuda:
+            comm_stream.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(comm_stream):
+                works = [dist.all_gather_into_tensor(staged_i, send_i, group=group, async_op=True),
+                         dist.all_gather_into_tensor(staged_d, send_d, group=group, async_op=True)]
+        else:
+            works = [dist.all_gather_into_tensor(staged_i, send_i, group=group, async_op=True),
+                     dist.all_gather_into_tensor(staged_d, send_d, group=group, async_op=True)]
+        groups.append((works, staged_i, staged_d, m, c, send_i, send_d))
+        if c > 0 and groups[c - 1] is not None:
+            place(groups[c - 1])
+    if groups and groups[-1] is not None:
+        place(groups[-1])
+    if cuda:
+        torch.cuda.current_stream(dev).wait_stream(place_stream)
+        torch.cuda.current_stream(dev).wait_stream(comm_stream)
+    return full_idx, full_dsq
+
+
 def sharded_binned_select_knn(K, coords, row_splits, direction=None, torch_compatible_indices=False,
                               group=None, gather=True, knn_fn: Optional[Callable] = None,
-                              replace_fn: Optional[Callable] = None, root=0, n_chunks=1, check=True):
+                              replace_fn: Optional[Callable] = None, root=0, n_chunks=1, check=True,
+                              exchange="auto"):
     """binned_select_knn over a batch that every rank holds, each rank searching its own events.
 
     gather = True / "all": (idx, distsq) of the whole batch on every rank; "root": on ``root``
@@ -317,6 +396,9 @@ def sharded_binned_select_knn(K, coords, row_splits, direction=None, torch_compa
     on receipt: a third fewer bytes on the links.  With n_chunks > 1 a rank searches its events
     in that many groups and the rows of a finished group travel while the next one is searched.
     check=False skips the agreement step (a 4-byte all-reduce and a host read).
+    exchange: how the rows reach every rank with gather="all" -- "collective" (one all-gather per
+    group into a staging buffer, then a placing pass; the default, "auto") or "p2p" (per-event
+    point-to-point blocks straight into the final tensors, which is what gather="root" always uses).
     """
     if not dist.is_initialized():
         raise RuntimeError("torch.distributed is not initialised")
@@ -335,6 +417,13 @@ def sharded_binned_select_knn(K, coords, row_splits, direction=None, torch_compa
                         "rank %d: the partition table covers %d rows, the batch has %d"
                         % (rank, sum(part.points), coords.shape[0]), coords.device, group)
     chunks = [chunk_events(part.events[r], row_splits, n_chunks) for r in range(world)]
+    if exchange not in ("auto", "collective", "p2p"):
+        raise ValueError("exchange must be 'auto', 'collective' or 'p2p'")
+    if mode == "all" and exchange in ("auto", "collective"):
+        def search(events):
+            return local_binned_select_knn(K, coords, row_splits, events, direction, torch_compatible_indices,
+                                           knn_fn, replace_fn)
+        return _gather_all_collective(K, coords, row_splits, chunks, search, group, rank, world)
     ex = EventRowExchange(row_splits, part, [(torch.int32, (K,), coords.device), (torch.float32, (K,), coords.device)],
                           mode, root, group)
     # the public ids are int64: a finished group is widened on a stream of its own while the

@@ -113,6 +113,11 @@ def _worker(rank, world, port, fail_rank, out):
                                                       replace_fn=_cpu_replace)
             assert idx2.dtype == torch.int64
             parity.assert_knn_parity(idx2.numpy(), dsq2.numpy(), ref_idx.numpy(), ref_d.numpy())
+            # the point-to-point exchange for rows on every rank (the default is the collective one)
+            idx3, dsq3 = es.sharded_binned_select_knn(9, coords, rs, n_chunks=2, knn_fn=_cpu_knn,
+                                                      replace_fn=_cpu_replace, exchange="p2p")
+            assert idx3.dtype == torch.int64
+            parity.assert_knn_parity(idx3.numpy(), dsq3.numpy(), ref_idx.numpy(), ref_d.numpy())
             # and gathered on rank 1 only
             ridx, rdsq = es.sharded_binned_select_knn(9, coords, rs, gather="root", root=1, knn_fn=_cpu_knn,
                                                       replace_fn=_cpu_replace)
