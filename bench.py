@@ -231,7 +231,15 @@ def run_b200(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        pg_options = None
+        if os.environ.get("FGC_BENCH_NCCL_HIGH_PRIORITY", "1") != "0":
+            # the exchange of finished rows runs beside the search of the next group, which fills
+            # every SM: NCCL's kernels get their CTAs sooner from a high-priority stream
+            try:
+                pg_options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+            except Exception:             # noqa: BLE001
+                pg_options = None
+        dist.init_process_group("nccl", device_id=dev, pg_options=pg_options)
 
     import fastgraphcompute_b200 as fgc
     from fastgraphcompute_b200 import _cabi, synthetic
