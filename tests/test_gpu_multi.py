@@ -38,6 +38,14 @@ def _worker(rank, world, port, out):
         # shard builds its own grid)
         same = torch.equal(torch.sort(dsq, 1).values, torch.sort(ref_dsq, 1).values) and \
             torch.equal(torch.sort(idx, 1).values, torch.sort(ref_idx, 1).values)
+        # the point-to-point form of the exchange and the gather to one rank give the same rows
+        pidx, pdsq = es.sharded_binned_select_knn(w.K, coords, rs, n_chunks=3, exchange="p2p")
+        def same_rows(i2, d2):
+            return torch.equal(torch.sort(d2, 1).values, torch.sort(ref_dsq, 1).values) and \
+                torch.equal(torch.sort(i2, 1).values, torch.sort(ref_idx, 1).values)
+        same = same and same_rows(pidx, pdsq)
+        ridx, rdsq = es.sharded_binned_select_knn(w.K, coords, rs, gather="root", root=1)
+        same = same and ((ridx is None and rdsq is None) if rank != 1 else same_rows(ridx, rdsq))
         part = es.partition_events(w.row_splits, world)
         # data-parallel GravNet step over the event shards: summed parameter gradients must equal
         # the gradients of the whole batch on one GPU
