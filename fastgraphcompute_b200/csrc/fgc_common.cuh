@@ -111,6 +111,15 @@ __device__ __forceinline__ void unpack_f32x2(unsigned long long v, float &a, flo
 {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
 }
+// Programmatic dependent launch (sm_90+): a kernel launched with launch_chained() may be scheduled
+// while its predecessor in the stream still runs; its CTAs then sit in chain_wait() until the
+// predecessor has finished and its writes are visible.  A predecessor lets that happen by calling
+// chain_release() (every CTA, as early as it likes).  Both are no-ops for a kernel launched the
+// plain way or without a kernel in front of it.  Used for chains of short kernels, where the
+// launch latency of each link is a tenth of its run time.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Index of the row split that contains point v: number of entries rs[1..] <= v
 // (what the reference finds by a linear scan, bin_by_coordinates_cpu.cpp:68-74).
 __device__ __forceinline__ int row_split_of(const int64_t *__restrict__ rs, int n_rs, int64_t v)
@@ -121,6 +130,23 @@ __device__ __forceinline__ int row_split_of(const int64_t *__restrict__ rs, int 
         if (rs[mid] > v) hi = mid; else lo = mid + 1;
     }
     return lo - 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 }  // namespace fgc

@@ -53,6 +53,8 @@ k_minmax_setup(const float *__restrict__ coords, int n_vert, int n_coords, int n
                int *__restrict__ counts, long long n_counts, const int64_t *__restrict__ row_splits, int n_rs,
                int bins_target, int bins_cap_first, int bins_cap)
 {
+    chain_wait();
+    chain_release();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_counts;
          i += (long long)gridDim.x * blockDim.x)
         counts[i] = 0;
@@ -269,6 +271,8 @@ __device__ void grid_refine(KnnGrid *g, unsigned long long sum_sq, int n_vert, f
 __global__ void __launch_bounds__(256)
 k_zero_counts(int *__restrict__ counts, const KnnGrid *g, int stage)
 {
+    chain_wait();
+    chain_release();
     if (g->refined < stage) return;      // stage s follows the s-th density pass that changed the grid
     const int n = g->total_bins + 1;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
@@ -295,6 +299,8 @@ k_histogram(const float *__restrict__ coords, int n_vert, int n_coords,
             int stage, int refine_pass, float seen_target, float seen_target3, int bins_target3,
             int allow_fallback)
 {
+    chain_wait();
+    chain_release();
     if (g->refined < stage) return;
     if (refine_pass == 1 && !g->fallback3) refine_pass = -1;
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
@@ -353,6 +359,8 @@ __global__ void __launch_bounds__(256)
 k_fill_ids(int n_vert, const KnnGrid *__restrict__ g, const int *__restrict__ bounds,
            const int *__restrict__ pbin, const int *__restrict__ prank, int *__restrict__ stmp)
 {
+    chain_wait();
+    chain_release();
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= n_vert || g->status != 0) return;
     const int pos = bounds[pbin[v]] + prank[v];
@@ -398,6 +406,8 @@ k_rank_place(const float *__restrict__ coords, int n_vert, int n_coords, int nv,
              int *__restrict__ sorig, float4 *__restrict__ scoords, int *__restrict__ sbin,
              uint8_t *__restrict__ sflag, int *__restrict__ biglist, int *__restrict__ hugelist)
 {
+    chain_wait();
+    chain_release();
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= n_vert || g->status != 0) return;
     const int bin = pbin[v];
@@ -433,6 +443,8 @@ k_sort_large_cells(const float *__restrict__ coords, int n_coords, int nv,
                    int *__restrict__ sorig, float4 *__restrict__ scoords, int *__restrict__ sbin,
                    uint8_t *__restrict__ sflag)
 {
+    chain_wait();
+    chain_release();
     __shared__ int s_keys[kSortWarps][kWarpSortMaxShared];
     if (g->status != 0) return;
     if ((int)blockIdx.x < n_warp_blocks) {
@@ -625,39 +637,33 @@ extern "C" int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int3
                                               bins_target, bins_cap_first, bins_cap);
     FGC_CHECK_LAUNCH();
     const int allow_fallback = adaptive && n_coords == 4 && forced == 0;
-    k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts, pbin, prank, 0,
-                                          adaptive ? 0 : -1, seen_target, seen_target3, bins_target, allow_fallback);
-    FGC_CHECK_LAUNCH();
+    FGC_RETURN_IF_CUDA(launch_chained(k_histogram, pt_blocks, 256, 0, s, coords, n, n_coords, row_splits, (int)n_rs, grid,
+                                      counts, pbin, prank, 0, adaptive ? 0 : -1, seen_target, seen_target3,
+                                      bins_target, allow_fallback));
     if (adaptive) {
         // the grid of the density pass, when it chose one (both kernels return at once otherwise)
-        k_zero_counts<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, 1);
-        FGC_CHECK_LAUNCH();
-        k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts, pbin, prank,
-                                              1, allow_fallback ? 1 : -1, seen_target, seen_target3, bins_target, 0);
-        FGC_CHECK_LAUNCH();
+        FGC_RETURN_IF_CUDA(launch_chained(k_zero_counts, fgc::sm_count() * 4, 256, 0, s, counts, grid, 1));
+        FGC_RETURN_IF_CUDA(launch_chained(k_histogram, pt_blocks, 256, 0, s, coords, n, n_coords, row_splits, (int)n_rs,
+                                          grid, counts, pbin, prank, 1, allow_fallback ? 1 : -1, seen_target,
+                                          seen_target3, bins_target, 0));
         if (allow_fallback) {
             // second density pass: ran only when the first one fell back to three coordinates
-            k_zero_counts<<<fgc::sm_count() * 4, 256, 0, s>>>(counts, grid, 2);
-            FGC_CHECK_LAUNCH();
-            k_histogram<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, row_splits, (int)n_rs, grid, counts, pbin,
-                                                  prank, 2, -1, seen_target, seen_target3, bins_target, 0);
-            FGC_CHECK_LAUNCH();
+            FGC_RETURN_IF_CUDA(launch_chained(k_zero_counts, fgc::sm_count() * 4, 256, 0, s, counts, grid, 2));
+            FGC_RETURN_IF_CUDA(launch_chained(k_histogram, pt_blocks, 256, 0, s, coords, n, n_coords, row_splits,
+                                              (int)n_rs, grid, counts, pbin, prank, 2, -1, seen_target, seen_target3,
+                                              bins_target, 0));
         }
     }
-    k_scan_tile_sums_top<<<scan_blocks, 256, 0, s>>>(counts, &grid->total_bins, 1, blocksums, &grid->scan_ticket);
-    FGC_CHECK_LAUNCH();
-    k_scan_apply<<<scan_blocks, 256, 0, s>>>(counts, &grid->total_bins, 1, blocksums);
-    FGC_CHECK_LAUNCH();
-    k_fill_ids<<<pt_blocks, 256, 0, s>>>(n, grid, counts, pbin, prank, stmp);
-    FGC_CHECK_LAUNCH();
-    k_rank_place<<<pt_blocks, 256, 0, s>>>(coords, n, n_coords, L.nv, direction_or_null, grid, counts, pbin,
-                                           prank, stmp, sorig, scoords, sbin, sflag, biglist, hugelist);
-    FGC_CHECK_LAUNCH();
+    FGC_RETURN_IF_CUDA(launch_chained(k_scan_tile_sums_top, scan_blocks, 256, 0, s, counts, &grid->total_bins, 1,
+                                      blocksums, &grid->scan_ticket));
+    FGC_RETURN_IF_CUDA(launch_chained(k_scan_apply, scan_blocks, 256, 0, s, counts, &grid->total_bins, 1, blocksums));
+    FGC_RETURN_IF_CUDA(launch_chained(k_fill_ids, pt_blocks, 256, 0, s, n, grid, counts, pbin, prank, stmp));
+    FGC_RETURN_IF_CUDA(launch_chained(k_rank_place, pt_blocks, 256, 0, s, coords, n, n_coords, L.nv, direction_or_null,
+                                      grid, counts, pbin, prank, stmp, sorig, scoords, sbin, sflag, biglist, hugelist));
     const int n_warp_blocks = fgc::sm_count() * 4;
-    k_sort_large_cells<<<n_warp_blocks + fgc::sm_count(), kSortWarps * 32, 0, s>>>(
-        coords, n_coords, L.nv, direction_or_null, grid, counts, biglist, hugelist, n_warp_blocks, sorig,
-        scoords, sbin, sflag);
-    FGC_CHECK_LAUNCH();
+    FGC_RETURN_IF_CUDA(launch_chained(k_sort_large_cells, n_warp_blocks + fgc::sm_count(), kSortWarps * 32, 0, s, coords,
+                                      n_coords, L.nv, direction_or_null, grid, counts, biglist, hugelist, n_warp_blocks,
+                                      sorig, scoords, sbin, sflag));
     return FGC_OK;
 }
 

@@ -47,6 +47,8 @@ static __global__ void __launch_bounds__(256)
 k_scan_tile_sums_top(const int *__restrict__ counts, const int *__restrict__ n_ptr, int n_add,
                      int *__restrict__ blocksums, int *ticket)
 {
+    chain_wait();
+    chain_release();
     const int n = scan_length(n_ptr, n_add);
     const int base = blockIdx.x * kScanTile;
     __shared__ int ws[8];
@@ -143,6 +145,8 @@ static __global__ void __launch_bounds__(256)
 k_scan_apply(int *__restrict__ counts, const int *__restrict__ n_ptr, int n_add,
              const int *__restrict__ blocksums)
 {
+    chain_wait();
+    chain_release();
     const int n = scan_length(n_ptr, n_add);
     const int base = blockIdx.x * kScanTile;
     if (base >= n) return;
