@@ -501,6 +501,8 @@ k_sort_large_cells(const float *__restrict__ coords, int n_coords, int nv,
 // Status word and the grid's form ((3 or 4) + 16 * fallback3) to memory the host can read.
 __global__ void k_publish_grid_info(const KnnGrid *__restrict__ g, volatile int32_t *info_mapped)
 {
+    chain_wait();
+    chain_release();
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         info_mapped[0] = g->status;
         info_mapped[1] = g->gdims + 16 * g->fallback3;
@@ -548,8 +550,8 @@ extern "C" int fgc_publish_status(const void *workspace_or_params, int32_t *stat
 extern "C" int fgc_knn_publish_grid_info(const void *workspace, int32_t *info_mapped, fgc_stream_t stream)
 {
     if (!workspace || !info_mapped) return FGC_ERR_BAD_ARGUMENT;
-    fgc::k_publish_grid_info<<<1, 32, 0, (cudaStream_t)stream>>>((const fgc::KnnGrid *)workspace, info_mapped);
-    FGC_CHECK_LAUNCH();
+    FGC_RETURN_IF_CUDA(fgc::launch_chained(fgc::k_publish_grid_info, 1, 32, 0, (cudaStream_t)stream,
+                                           (const fgc::KnnGrid *)workspace, info_mapped));
     return FGC_OK;
 }
 
@@ -578,7 +580,7 @@ extern "C" int fgc_knn_build_grid_dims(const float *coords, int64_t n_vert, int3
     cudaStream_t s = (cudaStream_t)stream;
     char *ws = (char *)workspace;
     KnnGrid *grid = (KnnGrid *)(ws + L.header);
-    FGC_RETURN_IF_CUDA(cudaMemsetAsync(grid, 0, kGridHeaderBytes, s));
+    FGC_RETURN_IF_CUDA(cudaMemsetAsync(grid, 0, kGridHeaderBytes + kHardTicketBytes, s));   // header and k_knn_hard's tickets
     if (n_vert == 0) return FGC_OK;
     if (!coords || n_rs < 2) return FGC_ERR_BAD_ARGUMENT;
 

@@ -144,12 +144,15 @@ __host__ __device__ inline void shell_item_decode4(int d, int u, int &o0, int &o
 constexpr int kRankMax = 32;
 
 constexpr size_t kGridHeaderBytes = 256;
+// one int per query that k_knn_hard splits over several CTAs (at most as many as the launch has CTAs)
+constexpr int kHardTickets = 1024;
+constexpr size_t kHardTicketBytes = sizeof(int32_t) * kHardTickets;
 static_assert(sizeof(KnnGrid) <= kGridHeaderBytes, "grid header too large");
 
 
 // Byte offsets of the workspace sections (all 256-byte aligned).
 struct KnnWorkspace {
-    size_t header, counts, blocksums, pbin, prank, stmp, sorig, sbin, sflag, biglist, hugelist, scoords, total;
+    size_t header, tickets, counts, blocksums, pbin, prank, stmp, sorig, sbin, sflag, biglist, hugelist, scoords, total;
     int64_t cap_bins;   // capacity of the cell table (entries), host decision
     int nv;             // float4 per point in the sorted coordinate array
 };
@@ -166,6 +169,7 @@ inline KnnWorkspace knn_workspace_layout(int64_t n_vert, int n_coords, int64_t n
     w.nv = (n_coords + 3) / 4;
     size_t off = 0;
     w.header = off; off += kGridHeaderBytes;
+    w.tickets = off; off += kHardTicketBytes;     // cleared together with the header
     w.counts = off; off = align_up(off + sizeof(int32_t) * (size_t)(cap + 1), 256);
     w.blocksums = off; off = align_up(off + sizeof(int32_t) * (size_t)((cap + 1) / kScanTile + 2), 256);
     w.pbin = off; off = align_up(off + sizeof(int32_t) * (size_t)n_vert, 256);

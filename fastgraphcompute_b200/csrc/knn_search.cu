@@ -646,6 +646,8 @@ template <int NV, int R>
 __global__ void __launch_bounds__(kKnnWarps * 32)
 k_knn_hard(const KnnArgs a)
 {
+    chain_wait();
+    chain_release();
     __shared__ float s_d[kKnnWarps][R * 32];
     __shared__ int s_i[kKnnWarps][R * 32];
     const int lane = threadIdx.x & 31;
@@ -662,7 +664,7 @@ k_knn_hard(const KnnArgs a)
     if (S > kHardMaxSplit) S = kHardMaxSplit;
     const long long cap = (long long)(a.hard_parts_bytes / kPartBytes) / n_hard;
     if (S > cap) S = cap;
-    if (S < 1 || n_hard > 1024 || !a.hard_parts || !a.hard_tickets) S = 1;     // (1024 tickets are cleared per search)
+    if (S < 1 || n_hard > kHardTickets || !a.hard_parts || !a.hard_tickets) S = 1;
     const int split = (int)S;
     const long long units = (long long)n_hard * split;
     float *__restrict__ part_d = a.hard_parts;
@@ -775,6 +777,8 @@ template <int NV, int R, bool COUNT, int MODE>
 __global__ void __launch_bounds__(kKnnWarps * 32, (R == 1 ? 8 : (R == 2 ? (NV == 1 ? 7 : 6) : (R == 4 ? 6 : 4))))
 k_knn(const KnnArgs a)
 {
+    chain_wait();
+    chain_release();
     if (MODE == 0) knn_query<NV, R, COUNT, false>(a);
     else if (MODE == 1) knn_query<NV, R, COUNT, true>(a);
     else if (a.grid->gdims == 4) knn_query<NV, R, COUNT, true>(a);
@@ -789,23 +793,23 @@ static int launch_knn_nv(const KnnArgs &a, cudaStream_t s)
     const int R = (kn + 31) / 32;
     const int T = kKnnWarps * 32;
     if (a.count_evals) {
-        if (R <= 1) k_knn<NV, 1, true, G4><<<blocks, T, 0, s>>>(a);
-        else if (R <= 2) k_knn<NV, 2, true, G4><<<blocks, T, 0, s>>>(a);
-        else if (R <= 4) k_knn<NV, 4, true, G4><<<blocks, T, 0, s>>>(a);
-        else k_knn<NV, 8, true, G4><<<blocks, T, 0, s>>>(a);
+        if (R <= 1) FGC_RETURN_IF_CUDA(launch_chained(k_knn<NV, 1, true, G4>, blocks, T, 0, s, a));
+        else if (R <= 2) FGC_RETURN_IF_CUDA(launch_chained(k_knn<NV, 2, true, G4>, blocks, T, 0, s, a));
+        else if (R <= 4) FGC_RETURN_IF_CUDA(launch_chained(k_knn<NV, 4, true, G4>, blocks, T, 0, s, a));
+        else FGC_RETURN_IF_CUDA(launch_chained(k_knn<NV, 8, true, G4>, blocks, T, 0, s, a));
     } else {
-        if (R <= 1) k_knn<NV, 1, false, G4><<<blocks, T, 0, s>>>(a);
-        else if (R <= 2) k_knn<NV, 2, false, G4><<<blocks, T, 0, s>>>(a);
-        else if (R <= 4) k_knn<NV, 4, false, G4><<<blocks, T, 0, s>>>(a);
-        else k_knn<NV, 8, false, G4><<<blocks, T, 0, s>>>(a);
+        if (R <= 1) FGC_RETURN_IF_CUDA(launch_chained(k_knn<NV, 1, false, G4>, blocks, T, 0, s, a));
+        else if (R <= 2) FGC_RETURN_IF_CUDA(launch_chained(k_knn<NV, 2, false, G4>, blocks, T, 0, s, a));
+        else if (R <= 4) FGC_RETURN_IF_CUDA(launch_chained(k_knn<NV, 4, false, G4>, blocks, T, 0, s, a));
+        else FGC_RETURN_IF_CUDA(launch_chained(k_knn<NV, 8, false, G4>, blocks, T, 0, s, a));
     }
     FGC_CHECK_LAUNCH();
     // the queries that gave up their walk (usually none: the CTAs return at once)
     const unsigned hard_blocks = fgc::sm_count() * 2;
-    if (R <= 1) k_knn_hard<NV, 1><<<hard_blocks, T, 0, s>>>(a);
-    else if (R <= 2) k_knn_hard<NV, 2><<<hard_blocks, T, 0, s>>>(a);
-    else if (R <= 4) k_knn_hard<NV, 4><<<hard_blocks, T, 0, s>>>(a);
-    else k_knn_hard<NV, 8><<<hard_blocks, T, 0, s>>>(a);
+    if (R <= 1) FGC_RETURN_IF_CUDA(launch_chained(k_knn_hard<NV, 1>, hard_blocks, T, 0, s, a));
+    else if (R <= 2) FGC_RETURN_IF_CUDA(launch_chained(k_knn_hard<NV, 2>, hard_blocks, T, 0, s, a));
+    else if (R <= 4) FGC_RETURN_IF_CUDA(launch_chained(k_knn_hard<NV, 4>, hard_blocks, T, 0, s, a));
+    else FGC_RETURN_IF_CUDA(launch_chained(k_knn_hard<NV, 8>, hard_blocks, T, 0, s, a));
     return (int)cudaGetLastError();
 }
 }  // namespace fgc
@@ -832,9 +836,9 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     a.sflag = has_direction ? (const uint8_t *)(ws + L.sflag) : nullptr;
     a.bounds = (const int *)(ws + L.counts);
     a.hardlist = (int *)(ws + L.stmp);        // free since the grid build
-    a.hard_parts = (float *)(ws + L.pbin);    // (so are pbin and prank)
+    a.hard_parts = (float *)(ws + L.pbin);    // (so is pbin)
     a.hard_parts_bytes = sizeof(int32_t) * (size_t)n_vert;
-    a.hard_tickets = (int *)(ws + L.prank);
+    a.hard_tickets = (int *)(ws + L.tickets);
     a.grid = (KnnGrid *)(ws + L.header);
     a.out_idx = out_idx;
     a.out_dist = out_distsq;
@@ -846,9 +850,12 @@ extern "C" int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, in
     // Every search starts its own list of queries for k_knn_hard: a grid may be searched more
     // than once (the build/search split), and a count left by an earlier search would make
     // this one re-scan stale entries and append behind them.
-    FGC_RETURN_IF_CUDA(cudaMemsetAsync(&a.grid->n_hard, 0, sizeof(int32_t), s));
-    // (one ticket per listed query that is split over several CTAs: fewer than the CTAs of the launch)
-    FGC_RETURN_IF_CUDA(cudaMemsetAsync(a.hard_tickets, 0, sizeof(int32_t) * (size_t)(n_vert < 1024 ? n_vert : 1024), s));
+    // The grid build leaves both cleared, so the first search of a grid (FGC_SEARCH_FRESH) needs
+    // no clearing and stays in the launch chain of the build.
+    if (!(flags & FGC_SEARCH_FRESH)) {
+        FGC_RETURN_IF_CUDA(cudaMemsetAsync(&a.grid->n_hard, 0, sizeof(int32_t), s));
+        FGC_RETURN_IF_CUDA(cudaMemsetAsync(a.hard_tickets, 0, kHardTicketBytes, s));
+    }
     if (n_coords <= 3) return launch_knn_nv<1, 0>(a, s);
     if (L.nv == 1) {
         // D = 4: a caller that fixed the grid's form at build time says so here too and gets the
@@ -871,6 +878,6 @@ extern "C" int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n
     int rc = fgc_knn_build_grid(coords, n_vert, n_coords, row_splits, n_rs, K, direction_or_null,
                                 target_occupancy, workspace, workspace_bytes, stream);
     if (rc != FGC_OK) return rc;
-    return fgc_knn_search(n_vert, n_coords, n_rs, K, direction_or_null != nullptr, tf_compat, 0,
+    return fgc_knn_search(n_vert, n_coords, n_rs, K, direction_or_null != nullptr, tf_compat, FGC_SEARCH_FRESH,
                           out_idx, out_distsq, workspace, workspace_bytes, stream);
 }

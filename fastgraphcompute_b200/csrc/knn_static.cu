@@ -65,7 +65,7 @@ extern "C" int fgc_binned_knn_fwd_static(const float *coords, int64_t n_vert, in
     rc = fgc_knn_build_grid(coords, n_vert, n_coords, row_splits, n_rs, K, direction_or_null,
                             target_occupancy, scratch, FGC_STATIC_WORKSPACE_BYTES, stream);
     if (rc != FGC_OK) return rc;
-    rc = fgc_knn_search(n_vert, n_coords, n_rs, K, direction_or_null != nullptr, tf_compat, 0, out_idx,
+    rc = fgc_knn_search(n_vert, n_coords, n_rs, K, direction_or_null != nullptr, tf_compat, FGC_SEARCH_FRESH, out_idx,
                         out_distsq, scratch, FGC_STATIC_WORKSPACE_BYTES, stream);
     if (rc != FGC_OK) return rc;
     // the status word is the first word of the scratch area: hand it to the caller's buffer

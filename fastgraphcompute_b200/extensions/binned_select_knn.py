@@ -100,7 +100,7 @@ def knn_forward_raw(coords, row_splits, K, direction, tf_compat, count_evals=Fal
             status_ready.record()
         _cabi.check(_cabi.lib.fgc_knn_search(
             n_vert, n_coords, n_rs, K, int(direction is not None), int(bool(tf_compat)),
-            (1 if count_evals else 0) | (8 if form == 3 else 16 if form == 4 else 0),
+            (1 if count_evals else 0) | (8 if form == 3 else 16 if form == 4 else 0) | 32,   # 32: first search of this grid
             _cabi.ptr(idx), _cabi.ptr(dist),
             _cabi.ptr(ws), nbytes, stream), "fgc_knn_search")
         if status_host is not None:

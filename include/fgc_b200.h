@@ -160,7 +160,9 @@ int fgc_binned_knn_fwd(const float *coords, int64_t n_vert, int32_t n_coords,
  * the debug counters in the workspace (fgc_knn_read_counters).  A built grid may be searched
  * any number of times (other K is not allowed: the workspace layout depends on the arguments).
  * Two searches of one workspace must not overlap in time (they share the list of queries that
- * gave up their walk and its scratch, which a search clears when it starts).
+ * gave up their walk and its scratch, which a search clears when it starts -- FGC_SEARCH_FRESH
+ * says that this is the first search since the grid was built, which left them cleared; the
+ * flag must not be given for a later search).
  *
  * When the status word of the workspace is non-zero after the grid build (non-finite
  * coordinate, malformed row_splits; see fgc_read_status) no neighbour is searched: every row
@@ -191,6 +193,7 @@ int fgc_knn_publish_grid_info(const void *workspace, int32_t *info_mapped, fgc_s
 #define FGC_SEARCH_COUNT 1     /* flags: accumulate the debug counters */
 #define FGC_SEARCH_GRID3 8     /* flags: the grid was built with grid_dims = 3 (D = 4) */
 #define FGC_SEARCH_GRID4 16    /* flags: the grid was built with grid_dims = 4 (D = 4) */
+#define FGC_SEARCH_FRESH 32    /* flags: first search of this workspace since fgc_knn_build_grid: nothing to clear */
 int fgc_knn_search(int64_t n_vert, int32_t n_coords, int64_t n_rs, int32_t K,
                    int32_t has_direction, int32_t tf_compat, int32_t flags,
                    int64_t *out_idx, float *out_distsq, void *workspace,
